@@ -8,7 +8,8 @@ cache needs (kv heads, head size, window) share one pool and one block table, an
 entry of the group stores its keys/values under the same page id in its own slice of the
 group's storage.  A group that keeps all keys holds a request's pages until it ends; a
 windowed group hands back pages that lie wholly behind the window while the request lives
-(table entry becomes the null page).  Freed pages go to the tail of the free queue, a
+(table entry becomes the null page), except the pages that hold the first ``keep_first`` tokens
+when the group's queries keep seeing those.  Freed pages go to the tail of the free queue, a
 finished request's pages in reverse order, so pages are used again.
 
 Tables are persistent numpy rows indexed by the request's state slot and updated
@@ -42,6 +43,7 @@ class CacheGroupSpec:
     heads: int                   # a page of a plane is [heads, page_size, width]
     width: int
     window: int | None = None
+    keep_first: int = 0          # first tokens of a request that stay visible behind the window
 
     @property
     def kind(self) -> str:
@@ -266,7 +268,8 @@ class KVManager:
 
     def advance(self, request_id: str, num_tokens: int) -> None:
         """Record that ``num_tokens`` more tokens are computed; windowed groups hand back the
-        pages that no later query can see (all positions < num_computed - window + 1)."""
+        pages that no later query can see (all positions < num_computed - window + 1, and none of
+        the group's kept first tokens)."""
         state = self._requests[request_id]
         state.num_computed += num_tokens
         for g, group in enumerate(self.groups):
@@ -281,12 +284,14 @@ class KVManager:
             first_visible = state.num_computed - group.window + 1
             releasable = max(first_visible, 0) // self.page_size
             releasable = min(releasable, state.num_blocks[g])
-            if releasable > state.num_released[g]:
+            # blocks below ``begin`` were handed back earlier or hold kept first tokens
+            begin = max(state.num_released[g], -(-group.keep_first // self.page_size))
+            if releasable > begin:
                 row = self.tables[g][state.slot]
-                pages = [int(p) for p in row[state.num_released[g] : releasable] if p != NULL_PAGE]
+                pages = [int(p) for p in row[begin:releasable] if p != NULL_PAGE]
                 self.pools[g].free(pages)
                 self._note_released(g, pages)
-                row[state.num_released[g] : releasable] = NULL_PAGE
+                row[begin:releasable] = NULL_PAGE
                 state.num_released[g] = releasable
                 self._touch(state.slot)
 
@@ -373,7 +378,7 @@ def group_entries(requirements) -> tuple[list[CacheGroupSpec], dict[int, int]]:
         if req.cache_spec is None or req.cache_of is not None:
             continue
         spec = req.cache_spec
-        by_spec.setdefault((spec.planes, spec.heads, spec.width, spec.window), []).append(req.entry)
+        by_spec.setdefault((spec.planes, spec.heads, spec.width, spec.window, spec.keep_first), []).append(req.entry)
     groups = [
         CacheGroupSpec(group_id, tuple(entries), *key)
         for group_id, (key, entries) in enumerate(by_spec.items())

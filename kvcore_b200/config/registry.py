@@ -3,7 +3,8 @@
 The reference keys its registry by ``model_type`` and maps to a model class
 (kvcore/model/model_loader/default_loader.py:32-36, 64-70).  Here the value is a function
 from the raw config.json dict to a ``ModelSpec``; the generic builder assembles the model
-from that.  The key is ``architectures[0]`` of config.json, with ``model_type`` as a fallback.
+from that.  The key is ``architectures[0]`` (or the string ``architecture``) of config.json, with
+``model_type`` as a fallback.
 """
 from __future__ import annotations
 
@@ -49,7 +50,7 @@ def registered_architectures() -> tuple[str, ...]:
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> ArchitectureEntry:
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for name in names:
@@ -82,6 +83,9 @@ def _register_stock_architectures() -> None:
         lambda raw: LlamaConfig.from_dict(raw).to_model_spec(),
         model_types=("llama",),
     )
+    from .toposun import ARCHITECTURE, ToposunConfig
+
+    register_architecture(ARCHITECTURE, lambda raw: ToposunConfig.from_dict(raw).to_model_spec())
 
 
 _register_stock_architectures()

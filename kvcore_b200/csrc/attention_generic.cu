@@ -1,8 +1,10 @@
 // Paged attention, general kernel: any head size up to 256, any head counts, any mix of
-// prompt portions and decode tokens, optional sliding window, float or bf16 storage.
+// prompt portions and decode tokens, optional sliding window (with an optional number of first
+// positions that stay visible behind it), float or bf16 storage.
 //
-// One warp owns one (token, query head) row and walks the request's keys from the first
-// visible position to the token's own position in steps of 32 keys: each lane scores one key
+// One warp owns one (token, query head) row and walks the request's keys (the kept first positions
+// that lie behind the window, then from the first position inside the window to the token's own) in
+// steps of 32 keys: each lane scores one key
 // (a full dot product over the head, in ascending order), the warp keeps a running maximum
 // and sum (online softmax, 32-bit), and every lane accumulates its own slice of the output
 // over the 32 values.  The walk depends only on the token's position, never on how the
@@ -40,8 +42,8 @@ paged_attention_rows_kernel(T* __restrict__ out, int out_stride, const T* __rest
                             const T* __restrict__ v_cache, const int* __restrict__ table,
                             int table_stride, const int* __restrict__ positions,
                             const int* __restrict__ req_index, int num_rows, int H, int KVH, int D,
-                            int page_size, int num_pages, float scale, int window, int vec,
-                            int* status) {
+                            int page_size, int num_pages, float scale, int window, int keep_first,
+                            int vec, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_ATTN_ROWS);
   __shared__ float q_smem[ATT_WARPS][ATT_MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -65,9 +67,13 @@ paged_attention_rows_kernel(T* __restrict__ out, int out_stride, const T* __rest
   const size_t page_elems = (size_t)KVH * page_size * D;
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
 
-  for (int base = first; base <= pos; base += 32) {
+  // two runs of keys: [0, kept) behind the window, then [first, pos]
+  const int kept = min(keep_first, first);
+  for (int run = kept > 0 ? 0 : 1; run < 2; ++run) {
+  const int run_lo = run == 0 ? 0 : first, run_hi = run == 0 ? kept : pos + 1;
+  for (int base = run_lo; base < run_hi; base += 32) {
     const int key = base + lane;
-    const bool valid = key <= pos;
+    const bool valid = key < run_hi;
     float score = -INFINITY;
     int page = 0;
     if (valid) {
@@ -89,7 +95,7 @@ paged_attention_rows_kernel(T* __restrict__ out, int out_stride, const T* __rest
     running_max = new_max;
 #pragma unroll
     for (int i = 0; i < SLICES; ++i) acc[i] *= correction;
-    const int count = min(32, pos - base + 1);
+    const int count = min(32, run_hi - base);
     for (int kk = 0; kk < count; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, p, kk);
       const int pg = __shfl_sync(0xffffffffu, page, kk);
@@ -101,6 +107,7 @@ paged_attention_rows_kernel(T* __restrict__ out, int out_stride, const T* __rest
         if (d < D) acc[i] = fmaf(pk, to_float(vrow[d]), acc[i]);
       }
     }
+  }
   }
   const float inv = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
   T* orow = out + (size_t)token * out_stride + (size_t)head * D;
@@ -115,12 +122,13 @@ extern "C" int kvb_paged_attention_rows(void* out, int out_stride, const void* q
                                         const void* k_cache, const void* v_cache, const int* table,
                                         int table_stride, const int* positions, const int* req_index,
                                         int tokens, int H, int KVH, int D, int page_size,
-                                        int num_pages, float scale, int window, int dtype,
-                                        cudaStream_t stream) {
+                                        int num_pages, float scale, int window, int keep_first,
+                                        int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   KVB_REQUIRE(D > 0 && D <= ATT_MAX_D, "paged_attention: head_dim must be in [1, 256]");
   KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "paged_attention: H must be a multiple of KVH");
   KVB_REQUIRE(page_size > 0 && num_pages > 1, "paged_attention: empty cache");
+  KVB_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "paged_attention: kept first positions need a window");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "paged_attention: no status word");
   const int esize = dtype == KVB_F32 ? 4 : 2;
@@ -132,12 +140,12 @@ extern "C" int kvb_paged_attention_rows(void* out, int out_stride, const void* q
     KVB_CHECK_CUDA(kvb_launch((paged_attention_rows_kernel<float>), dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, true, 
         (float*)out, out_stride, (const float*)q, q_stride, (const float*)k_cache,
         (const float*)v_cache, table, table_stride, positions, req_index, (int)rows, H, KVH, D,
-        page_size, num_pages, scale, window, vec, status));
+        page_size, num_pages, scale, window, keep_first, vec, status));
   else
     KVB_CHECK_CUDA(kvb_launch((paged_attention_rows_kernel<bf16>), dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, true, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)k_cache,
         (const bf16*)v_cache, table, table_stride, positions, req_index, (int)rows, H, KVH, D,
-        page_size, num_pages, scale, window, vec, status));
+        page_size, num_pages, scale, window, keep_first, vec, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }

@@ -142,6 +142,14 @@ struct KvbTrace {
 #define KVB_TAG_GEMM_STREAM 13
 #define KVB_TAG_SAMPLE 14
 #define KVB_TAG_FEED_TOKENS 16
+#define KVB_TAG_LAYERNORM 17
+#define KVB_TAG_STREAM_ADD 18
+#define KVB_TAG_QK_PREPARE 19
+#define KVB_TAG_GLU_CLAMPED 20
+#define KVB_TAG_MOE_ROUTE 21
+#define KVB_TAG_MOE_ALIGN 22
+#define KVB_TAG_MOE_GEMM 23
+#define KVB_TAG_MOE_COMBINE 24
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

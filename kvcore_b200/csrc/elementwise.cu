@@ -487,4 +487,42 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------
+// Clamped gated activation of a packed [T, 2I] tensor (gate columns [0, I), up columns [I, 2I)):
+//   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = g * sigmoid(alpha * g) * (u + shift)
+// in 32-bit, rounded once.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, float alpha,
+                                   float limit, float shift, long long total) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GLU_CLAMPED);
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += step) {
+    const long long row = i / inter;
+    const int col = (int)(i % inter);
+    const float g = fminf(to_float(gu[row * 2 * inter + col]), limit);
+    const float u = fminf(fmaxf(to_float(gu[row * 2 * inter + inter + col]), -limit), limit);
+    out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+  }
+}
+
+extern "C" int kvb_glu_clamped(void* out, const void* gate_up, int rows, int inter, float alpha, float limit,
+                               float shift, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  KVB_REQUIRE(inter > 0, "glu_clamped: width must be positive");
+  const long long total = (long long)rows * inter;
+  const int threads = 256;
+  const long long wanted = (total + threads - 1) / threads;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
+  const int blocks = (int)(wanted < resident ? wanted : resident);
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((glu_clamped_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true,
+                              (float*)out, (const float*)gate_up, inter, alpha, limit, shift, total));
+  else
+    KVB_CHECK_CUDA(kvb_launch((glu_clamped_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true,
+                              (bf16*)out, (const bf16*)gate_up, inter, alpha, limit, shift, total));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
 KVB_TRACE_TU(elementwise)

@@ -1,0 +1,158 @@
+// Everything between the q/k(/v) projection of a step's tokens and the attention over the paged
+// cache, in one kernel: an optional RMS norm of q and of k, a half-layout rotation of the first
+// `rot` entries of every head, the write of keys and values into their pages, and q back in place.
+//
+//   norm_mode 0: none.
+//   norm_mode 1: one root mean square over the whole projection (all heads of q at once, all heads of k
+//                at once), weights of the projection's size.
+//   norm_mode 2: one root mean square per head, weights of the head's size (shared by the heads).
+//   value_mode 0: values are the third section of the row (q heads, k heads, v heads).
+//   value_mode 1: values are the keys as projected, before the norm and the rotation (row: q heads, k heads).
+//
+// x * rsqrt(mean(x^2) + eps) * w, sums, angles and rotation are 32-bit; q, the key and the value are
+// rounded to the storage type once, at the end.  One block per token; a head's sum of squares is a
+// warp's butterfly over a lane-strided walk, and the whole-projection sum adds the heads' sums in
+// ascending order, so a token's result does not depend on the batch.
+// Cache layout [pages, KVH, page, D]; k_cache == nullptr: nothing is written.
+#include "common.cuh"
+
+#define QKP_THREADS 256
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(QKP_THREADS)
+qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restrict__ positions,
+                  const int* __restrict__ req_index, const float2* __restrict__ cos_sin,
+                  const W* __restrict__ q_weight, const W* __restrict__ k_weight,
+                  const int* __restrict__ table, int table_stride, T* __restrict__ k_cache,
+                  T* __restrict__ v_cache, int H, int KVH, int D, int rot, int norm_mode, int value_mode,
+                  float eps, int page_size, int num_pages, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_QK_PREPARE);
+  extern __shared__ float smem[];
+  const int heads = H + KVH;
+  float* x = smem;                       // [heads * D]: q heads then k heads, 32-bit
+  float* head_sq = smem + (size_t)heads * D;   // [heads]
+  float* inv = head_sq + heads;          // [heads]
+  const int token = blockIdx.x;
+  const int pos = positions[token];
+  T* row = rows + (size_t)token * row_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = QKP_THREADS / 32;
+
+  for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[i] = to_float(row[i]);
+  __syncthreads();
+
+  size_t cache_base = 0;
+  bool write = k_cache != nullptr;
+  if (write) {
+    const int page = table[(size_t)req_index[token] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      write = false;
+    }
+    cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
+  }
+  const size_t head_stride = (size_t)page_size * D;
+  if (write) {
+    const T* v = value_mode == 1 ? row + (size_t)H * D : row + (size_t)(H + KVH) * D;
+    for (int i = threadIdx.x; i < KVH * D; i += QKP_THREADS) {
+      const int vh = i / D, d = i % D;
+      v_cache[cache_base + (size_t)vh * head_stride + d] = v[i];
+    }
+  }
+
+  if (norm_mode != 0) {
+    for (int h = warp; h < heads; h += nwarps) {
+      float sq = 0.0f;
+      for (int d = lane; d < D; d += 32) { const float v = x[(size_t)h * D + d]; sq = fmaf(v, v, sq); }
+      sq = warp_sum(sq);
+      if (lane == 0) head_sq[h] = sq;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (norm_mode == 1) {
+        float q_sq = 0.0f, k_sq = 0.0f;
+        for (int h = 0; h < H; ++h) q_sq += head_sq[h];
+        for (int h = H; h < heads; ++h) k_sq += head_sq[h];
+        const float q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
+        const float k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
+        for (int h = 0; h < heads; ++h) inv[h] = h < H ? q_inv : k_inv;
+      } else {
+        for (int h = 0; h < heads; ++h) inv[h] = 1.0f / sqrtf(head_sq[h] / (float)D + eps);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
+      const int h = i / D, d = i % D;
+      float w;
+      if (norm_mode == 1) w = h < H ? to_float(q_weight[i]) : to_float(k_weight[i - H * D]);
+      else w = h < H ? to_float(q_weight[d]) : to_float(k_weight[d]);
+      x[i] = x[i] * inv[h] * w;
+    }
+    __syncthreads();
+  }
+
+  const int half = rot >> 1;
+  if (cos_sin != nullptr && half > 0) {
+    for (int item = threadIdx.x; item < heads * half; item += QKP_THREADS) {
+      const int h = item / half, j = item % half;
+      const float2 cs = cos_sin[(size_t)token * half + j];
+      float* p = x + (size_t)h * D;
+      const float a = p[j], b = p[j + half];
+      p[j] = a * cs.x - b * cs.y;
+      p[j + half] = b * cs.x + a * cs.y;
+    }
+    __syncthreads();
+  }
+
+  __syncthreads();   // the values were copied from the row that is overwritten now
+  for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
+    const T v = from_float<T>(x[i]);
+    row[i] = v;
+    if (i >= H * D && write) {
+      const int kh = (i - H * D) / D, d = (i - H * D) % D;
+      k_cache[cache_base + (size_t)kh * head_stride + d] = v;
+    }
+  }
+}
+
+extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* positions, const int* req_index,
+                              const float* cos_sin, const void* q_weight, const void* k_weight, const int* table,
+                              int table_stride, void* k_cache, void* v_cache, int tokens, int H, int KVH, int D,
+                              int rot, int norm_mode, int value_mode, float eps, int page_size, int num_pages,
+                              int dtype, int weight_dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  KVB_REQUIRE(D > 0 && H >= 0 && KVH >= 0 && H + KVH > 0, "qk_prepare: no heads");
+  KVB_REQUIRE(rot >= 0 && rot <= D && rot % 2 == 0, "qk_prepare: the rotated entries must be an even count within the head");
+  KVB_REQUIRE(norm_mode >= 0 && norm_mode <= 2, "qk_prepare: unknown norm mode");
+  KVB_REQUIRE(value_mode == 0 || value_mode == 1, "qk_prepare: unknown value mode");
+  KVB_REQUIRE(norm_mode == 0 || (q_weight != nullptr && (KVH == 0 || k_weight != nullptr)), "qk_prepare: a norm needs its weights");
+  KVB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "qk_prepare: give both caches or none");
+  KVB_REQUIRE(k_cache == nullptr || (table != nullptr && page_size > 0 && KVH > 0), "qk_prepare: a cache write needs a block table");
+  const long long needed = (long long)(H + KVH + (k_cache != nullptr && value_mode == 0 ? KVH : 0)) * D;
+  KVB_REQUIRE(row_stride >= needed, "qk_prepare: row stride is smaller than the row");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "qk_prepare: no status word");
+  const size_t smem = ((size_t)(H + KVH) * D + 2 * (size_t)(H + KVH)) * sizeof(float);
+  KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
+#define KVB_QKP(T_, W_)                                                                                     \
+  do {                                                                                                      \
+    if (smem > 48 * 1024)                                                                                   \
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(qk_prepare_kernel<T_, W_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    KVB_CHECK_CUDA(kvb_launch((qk_prepare_kernel<T_, W_>), dim3(tokens), dim3(QKP_THREADS), smem, stream, true, \
+                              (T_*)rows, row_stride, positions, req_index, (const float2*)cos_sin,          \
+                              (const W_*)q_weight, (const W_*)k_weight, table, table_stride, (T_*)k_cache,  \
+                              (T_*)v_cache, H, KVH, D, rot, norm_mode, value_mode, eps, page_size, num_pages, status)); \
+  } while (0)
+  if (dtype == KVB_F32) {
+    KVB_REQUIRE(weight_dtype == KVB_F32, "qk_prepare: a 32-bit model needs 32-bit norm weights");
+    KVB_QKP(float, float);
+  } else if (weight_dtype == KVB_F32) {
+    KVB_QKP(bf16, float);
+  } else {
+    KVB_QKP(bf16, bf16);
+  }
+#undef KVB_QKP
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+KVB_TRACE_TU(qk_prepare)

@@ -45,7 +45,16 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_rope_kv_write": [_vp, _ll, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                               _int, _int, _int, _vp],
         "kvb_paged_attention_rows": [_vp, _int, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int,
-                                     _int, _int, _int, _int, _float, _int, _int, _vp],
+                                     _int, _int, _int, _int, _float, _int, _int, _int, _vp],
+        "kvb_layer_norm": [_vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _int, _vp],
+        "kvb_stream_add": [_vp, _vp, _int, _vp, _vp, _ll, _int, _vp],
+        "kvb_qk_prepare": [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int, _int,
+                           _int, _int, _float, _int, _int, _int, _int, _vp],
+        "kvb_glu_clamped": [_vp, _vp, _int, _int, _float, _float, _float, _int, _vp],
+        "kvb_moe_route": [_vp, _vp, _vp, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _vp],
+        "kvb_moe_align": [_vp, _vp, _vp, _vp, _int, _int, _int, _vp],
+        "kvb_moe_gemm": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_moe_combine": [_vp, _vp, _int, _int, _vp, _vp, _int, _int, _int, _vp],
         "kvb_flash_paged_attention": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int,
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
@@ -78,6 +87,8 @@ def ensure_built(verbose: bool = False) -> str:
     lib.kvb_gemm_stream_norm_max_k.restype = _int
     lib.kvb_gemm_stream_scratch_marker.argtypes = []
     lib.kvb_gemm_stream_scratch_marker.restype = ctypes.c_uint
+    lib.kvb_moe_tile_rows.argtypes = []
+    lib.kvb_moe_tile_rows.restype = _int
     _lib = lib
     return str(path)
 
@@ -460,6 +471,7 @@ def paged_attention(
     use_tc5: bool = True,
     cos_sin: torch.Tensor | None = None,
     write_kv: bool | None = None,
+    keep_first: int = 0,
 ) -> torch.Tensor:
     """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
 
@@ -476,7 +488,7 @@ def paged_attention(
     """
     if write_kv is not None:
         group = num_heads // num_kv_heads
-        fused = (not force_general and use_tma and flash_attention_supported(qkv.dtype, head_dim)
+        fused = (not force_general and not keep_first and use_tma and flash_attention_supported(qkv.dtype, head_dim)
                  and qkv.stride(0) % 8 == 0 and ctx.max_query_len * group <= 16
                  and tma_decode_supported(qkv.dtype, head_dim, k_cache.shape[2]))
         if not fused:
@@ -496,8 +508,11 @@ def paged_attention(
     num_pages, kvh, page_size, d = k_cache.shape
     if (kvh, d) != (num_kv_heads, head_dim):
         raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match the head layout")
+    if keep_first < 0 or (keep_first and not window):
+        raise KernelError(f"kept first positions ({keep_first}) need a window")
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    if not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0:
+    if (not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0
+            and not keep_first):
         group = num_heads // num_kv_heads
         geometry = (num_heads, num_kv_heads, head_dim, float(scale), int(window or 0))
         # A mixed step (portions of prompts beside single decoded tokens) is two kinds of work: the
@@ -522,7 +537,8 @@ def paged_attention(
     _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
           ctx.positions.data_ptr(), ctx.req_index.data_ptr(), tokens, num_heads, num_kv_heads,
-          head_dim, page_size, num_pages, float(scale), int(window or 0), _dtype_code(qkv), _stream())
+          head_dim, page_size, num_pages, float(scale), int(window or 0), int(keep_first), _dtype_code(qkv),
+          _stream())
     return out
 
 
@@ -603,11 +619,12 @@ STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 _stream_scratch: dict[int, torch.Tensor] = {}
 
 
-TRACE_TAGS = {1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
+TRACE_TAGS = {17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+              22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
-                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream")
+                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe")
 _trace_buffer: torch.Tensor | None = None
 
 
@@ -847,6 +864,205 @@ def linear_add_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
     return linear(x, weight, bias), None
 
 
+# ---- parts of layers that keep a 32-bit residual stream -------------------------------------------
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
+               out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` over the last axis of ``x [rows, width]`` with
+    32-bit statistics; ``x`` may be the 32-bit stream of a bfloat16 model, ``out_dtype`` the activations'."""
+    _check(x, "x")
+    _check(weight, "weight")
+    rows, width = x.shape
+    if weight.numel() != width or (bias is not None and (bias.numel() != width or bias.dtype != weight.dtype)):
+        raise KernelError(f"layer_norm: weight/bias do not match rows of width {width}")
+    out = torch.empty((rows, width), dtype=out_dtype or x.dtype, device=x.device)
+    _call("kvb_layer_norm", out.data_ptr(), x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
+          rows, width, float(eps), _dtype_code(x), _dtype_code(out), _dtype_code(weight), _stream())
+    return out
+
+
+def stream_add(base: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tensor | None = None) -> torch.Tensor:
+    """The 32-bit residual stream: ``base + (a + b)`` summed in 32-bit.  A 32-bit ``base`` is updated in
+    place and returned; a ``base`` of the activation type (the embedded tokens) is widened into a new stream."""
+    _check(base, "base")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _check(t, name)
+            if t.shape != base.shape:
+                raise KernelError(f"stream_add: {name} {tuple(t.shape)} does not match the stream {tuple(base.shape)}")
+    if b is not None and (a is None or a.dtype != b.dtype):
+        raise KernelError("stream_add: the two addends must have one type")
+    out = base if base.dtype == torch.float32 else torch.empty(base.shape, dtype=torch.float32, device=base.device)
+    if a is None and base.dtype == torch.float32:
+        return out
+    addend = a if a is not None else base
+    _call("kvb_stream_add", out.data_ptr(), base.data_ptr(), _dtype_code(base), None if a is None else a.data_ptr(),
+          None if b is None else b.data_ptr(), base.numel(), _dtype_code(addend), _stream())
+    return out
+
+
+QK_NORM_MODES = {None: 0, "none": 0, "projection": 1, "head": 2}
+
+
+def qk_prepare(rows: torch.Tensor, positions: torch.Tensor, req_index: torch.Tensor, cos_sin: torch.Tensor | None,
+               table: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+               num_heads: int, num_kv_heads: int, head_dim: int, *, rotary_dim: int | None = None,
+               norm: str | None = None, q_norm_weight: torch.Tensor | None = None,
+               k_norm_weight: torch.Tensor | None = None, eps: float = 0.0, value_from_key: bool = False,
+               write_kv: bool = True) -> None:
+    """Norm of q and k (``norm``: None, "projection" = one root mean square over all heads of q and one
+    over all heads of k, "head" = one per head), rotation of the first ``rotary_dim`` entries of every head
+    with the ``[T, rotary_dim/2, 2]`` table ``cos_sin``, and the write of keys and values into their pages;
+    q and k of ``rows [T, (H+KVH(+KVH))*D]`` are replaced in place.  ``value_from_key``: the values are the
+    keys as projected (before norm and rotation) and ``rows`` has no value section."""
+    _check(rows, "rows", contiguous=False)
+    _check(positions, "positions", dtype=torch.int32)
+    _check(req_index, "req_index", dtype=torch.int32)
+    tokens = rows.shape[0]
+    if rows.stride(1) != 1:
+        raise KernelError("qk_prepare: rows must be contiguous")
+    sections = num_heads + num_kv_heads * (1 if value_from_key else 2)
+    if rows.shape[1] != sections * head_dim:
+        raise KernelError(f"qk_prepare: row width {rows.shape[1]} does not match the head layout")
+    rot = head_dim if rotary_dim is None else int(rotary_dim)
+    if cos_sin is None:
+        rot = 0
+    else:
+        _check(cos_sin, "cos_sin", dtype=torch.float32)
+        if tuple(cos_sin.shape) != (tokens, rot // 2, 2):
+            raise KernelError(f"cos_sin has shape {tuple(cos_sin.shape)} for {tokens} tokens and {rot} rotated entries")
+    mode = QK_NORM_MODES[norm]
+    weight_code = _dtype_code(rows)
+    if mode:
+        expect_q = num_heads * head_dim if mode == 1 else head_dim
+        expect_k = num_kv_heads * head_dim if mode == 1 else head_dim
+        _check(q_norm_weight, "q_norm_weight")
+        _check(k_norm_weight, "k_norm_weight", dtype=q_norm_weight.dtype)
+        if q_norm_weight.numel() != expect_q or k_norm_weight.numel() != expect_k:
+            raise KernelError("qk_prepare: norm weights do not match the head layout")
+        weight_code = _dtype_code(q_norm_weight)
+    k_ptr = v_ptr = table_ptr = None
+    table_stride = page_size = num_pages = 0
+    if write_kv:
+        if k_cache is None or v_cache is None or table is None:
+            raise KernelError("a cache write needs k_cache, v_cache and a block table")
+        _check(k_cache, "k_cache", dtype=rows.dtype)
+        _check(v_cache, "v_cache", dtype=rows.dtype)
+        _check(table, "block table", dtype=torch.int32, contiguous=False)
+        num_pages, kvh, page_size, d = k_cache.shape
+        if (kvh, d) != (num_kv_heads, head_dim) or v_cache.shape != k_cache.shape or table.stride(1) != 1:
+            raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match the head layout")
+        k_ptr, v_ptr, table_ptr, table_stride = k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0)
+    _call("kvb_qk_prepare", rows.data_ptr(), rows.stride(0), positions.data_ptr(), req_index.data_ptr(),
+          None if cos_sin is None else cos_sin.data_ptr(),
+          None if not mode else q_norm_weight.data_ptr(), None if not mode else k_norm_weight.data_ptr(),
+          table_ptr, table_stride, k_ptr, v_ptr, tokens, num_heads, num_kv_heads, head_dim, rot, mode,
+          int(bool(value_from_key)), float(eps), page_size, num_pages, _dtype_code(rows), weight_code, _stream())
+
+
+def glu_clamped(gate_up: torch.Tensor, *, alpha: float, limit: float, shift: float) -> torch.Tensor:
+    """``g * sigmoid(alpha * g) * (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``
+    of a packed ``[T, 2I]`` tensor (gate columns first)."""
+    _check(gate_up, "gate_up")
+    rows, two_inter = gate_up.shape
+    if two_inter % 2:
+        raise KernelError(f"gate_up must have an even width, got {two_inter}")
+    out = torch.empty((rows, two_inter // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _call("kvb_glu_clamped", out.data_ptr(), gate_up.data_ptr(), rows, two_inter // 2, float(alpha), float(limit),
+          float(shift), _dtype_code(gate_up), _stream())
+    return out
+
+
+MOE_SCORE_MODES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, score: str = "sigmoid", renormalize: bool = False,
+              gate_rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """Router of a mixture of experts on ``x [T, K]``: 32-bit logits with the 32-bit matrix ``router [E, K]``,
+    scores by ``score``, the ``top`` largest per token.  Returns ``(ids [T, top] int32, weights [T, top] float32,
+    gates)``; ``gates [T, R]`` = ``sigmoid(gate_rows @ x)`` for the 32-bit rows ``gate_rows [R, K]``, else None."""
+    _check(x, "x", contiguous=False)
+    _check(router, "router", dtype=torch.float32)
+    tokens, k = x.shape
+    experts = router.shape[0]
+    if router.shape[1] != k or x.stride(1) != 1:
+        raise KernelError(f"moe_route: x {tuple(x.shape)} does not match the router {tuple(router.shape)}")
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    gates, extra = None, 0
+    if gate_rows is not None:
+        _check(gate_rows, "gate_rows", dtype=torch.float32)
+        if gate_rows.dim() != 2 or gate_rows.shape[1] != k:
+            raise KernelError(f"moe_route: gate rows {tuple(gate_rows.shape)} do not match x")
+        extra = gate_rows.shape[0]
+        gates = torch.empty((tokens, extra), dtype=torch.float32, device=x.device)
+    _call("kvb_moe_route", ids.data_ptr(), weights.data_ptr(), None if gates is None else gates.data_ptr(),
+          x.data_ptr(), x.stride(0), router.data_ptr(), None if gate_rows is None else gate_rows.data_ptr(),
+          tokens, experts, extra, k, int(top), MOE_SCORE_MODES[score], int(bool(renormalize)), _dtype_code(x), _stream())
+    return ids, weights, gates
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
+                down: torch.Tensor, *, weight_on_input: bool) -> torch.Tensor:
+    """The chosen experts of every token: ``out [T * top, N]``, row ``t * top + s`` holding
+    ``down[e] @ (silu(gate[e] @ a) * (up[e] @ a))`` for ``e = ids[t, s]``.  ``weight_on_input``:
+    ``a = weights[t, s] * x[t]`` (rounded to the storage type).  Otherwise ``a = x[t]`` and the weight
+    multiplies the rows that enter the last product, which weights the output, that product being linear.
+    ``gate_up [E, 2F, K]`` (gate rows first), ``down [E, N, F]``."""
+    _check(x, "x", contiguous=False)
+    _check(ids, "ids", dtype=torch.int32)
+    _check(weights, "weights", dtype=torch.float32)
+    _check(gate_up, "gate_up", dtype=x.dtype)
+    _check(down, "down", dtype=x.dtype)
+    tokens, k = x.shape
+    top = ids.shape[1]
+    experts, two_ff, _ = gate_up.shape
+    ff = two_ff // 2
+    n = down.shape[1]
+    if gate_up.shape[2] != k or down.shape != (experts, n, ff) or x.stride(1) != 1:
+        raise KernelError("moe_experts: the experts' matrices do not match the input")
+    pairs = tokens * top
+    tile = int(_lib.kvb_moe_tile_rows()) if _lib is not None else 16
+    max_tiles = min(-(-(pairs + experts * (tile - 1)) // tile), pairs)
+    capacity = max_tiles * tile
+    sorted_pairs = torch.empty(capacity, dtype=torch.int32, device=x.device)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=x.device)
+    meta = torch.empty(4, dtype=torch.int32, device=x.device)
+    _call("kvb_moe_align", sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), ids.data_ptr(), pairs,
+          experts, capacity, _stream())
+    code = _dtype_code(x)
+    hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+    _call("kvb_moe_gemm", hidden.data_ptr(), x.data_ptr(), x.stride(0), top,
+          weights.data_ptr() if weight_on_input else None, gate_up.data_ptr(), sorted_pairs.data_ptr(),
+          tile_expert.data_ptr(), meta.data_ptr(), max_tiles, ff, k, 1, code, _stream())
+    out = torch.empty((pairs, n), dtype=x.dtype, device=x.device)
+    _call("kvb_moe_gemm", out.data_ptr(), hidden.data_ptr(), hidden.stride(0), 1,
+          None if weight_on_input else weights.data_ptr(), down.data_ptr(), sorted_pairs.data_ptr(),
+          tile_expert.data_ptr(), meta.data_ptr(), max_tiles, n, ff, 0, code, _stream())
+    return out
+
+
+def moe_combine(expert_out: torch.Tensor, tokens: int, top: int, shared: torch.Tensor | None = None,
+                gates: torch.Tensor | None = None) -> torch.Tensor:
+    """``y[t] = sum_s expert_out[t * top + s] (+ gates[t, 0] * shared[t])``, summed in 32-bit in slot order."""
+    _check(expert_out, "expert_out")
+    width = expert_out.shape[1]
+    if expert_out.shape[0] != tokens * top:
+        raise KernelError("moe_combine: one row per (token, slot) is needed")
+    if shared is not None:
+        _check(shared, "shared", dtype=expert_out.dtype)
+        if tuple(shared.shape) != (tokens, width):
+            raise KernelError("moe_combine: the shared expert's rows do not match")
+    if gates is not None:
+        _check(gates, "gates", dtype=torch.float32)
+        if shared is None or gates.shape[0] != tokens:
+            raise KernelError("moe_combine: gates need the shared rows they multiply")
+    out = torch.empty((tokens, width), dtype=expert_out.dtype, device=expert_out.device)
+    _call("kvb_moe_combine", out.data_ptr(), expert_out.data_ptr(), tokens, top,
+          None if shared is None else shared.data_ptr(), None if gates is None else gates.data_ptr(),
+          0 if gates is None else gates.stride(0), width, _dtype_code(expert_out), _stream())
+    return out
+
+
 def sample(logits: torch.Tensor, packed_params: torch.Tensor, eps: float) -> torch.Tensor:
     """One token per row of ``logits [S, V]`` float32; ``packed_params [S, 6]`` float64 (on the
     device already, or on the host: then copied): temperature, top_k, top_p, seed low 32 bits, seed
@@ -871,7 +1087,14 @@ __all__ = [
     "tc5_prefill_supported",
     "tma_decode_supported",
     "gather_rows",
+    "glu_clamped",
+    "layer_norm",
     "library_is_loaded",
+    "moe_combine",
+    "moe_experts",
+    "moe_route",
+    "qk_prepare",
+    "stream_add",
     "linear",
     "linear_add_residual",
     "linear_silu_mul",

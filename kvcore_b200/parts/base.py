@@ -65,23 +65,28 @@ class CacheSpec:
     ``kv_heads`` heads of ``head_dim`` (``CacheSpec.keys_and_values``); a mixer that caches one
     vector per token declares one plane of one head.  ``window`` is ``None`` when every cached
     token stays visible, else the number of trailing tokens a query sees; pages wholly behind the
-    window are handed back while the request lives.
+    window are handed back while the request lives.  ``keep_first``: that many first tokens of a request
+    stay visible behind the window (their pages are never handed back).
     """
 
     planes: int
     heads: int
     width: int
     window: int | None = None
+    keep_first: int = 0
 
     def __post_init__(self) -> None:
         if self.planes <= 0 or self.heads <= 0 or self.width <= 0:
             raise ValueError(f"a cache spec needs positive planes, heads and width, got {self}")
         if self.window is not None and self.window <= 0:
             raise ValueError(f"window must be positive when set, got {self.window}")
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            raise ValueError(f"keep_first must be >= 0 and needs a window, got {self.keep_first}")
 
     @classmethod
-    def keys_and_values(cls, num_kv_heads: int, head_dim: int, window: int | None = None) -> "CacheSpec":
-        return cls(2, int(num_kv_heads), int(head_dim), window)
+    def keys_and_values(cls, num_kv_heads: int, head_dim: int, window: int | None = None,
+                        keep_first: int = 0) -> "CacheSpec":
+        return cls(2, int(num_kv_heads), int(head_dim), window, int(keep_first))
 
     @property
     def elements_per_token(self) -> int:

@@ -1,4 +1,5 @@
-"""Arrangement of one layer: pre-norm mixer and feed-forward on a deferred residual.
+"""Arrangements of one layer: pre-norm mixer and feed-forward in sequence on a deferred residual, or side
+by side on a 32-bit stream.
 
 As the reference's decoder layer (kvcore/model/models/llama3.py:124-142): the running
 ``residual`` and the last sub-layer output ``h`` stay separate and are summed inside the
@@ -8,6 +9,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels as K
 from ..config.model_spec import LayerSpec
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Summed, WeightSlot
 
@@ -70,6 +72,46 @@ class PreNormResidualBlock(Block):
         return h, residual
 
 
-BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+class ParallelResidualBlock(Block):
+    """Mixer and feed-forward side by side on one stream: ``x <- x + (mixer(norm_a(x)) + ff(norm_b(x)))``,
+    both norms reading the same ``x``.  The stream ``x`` is kept in 32-bit whatever the activation type:
+    the two sub-layer outputs are added to each other and then to the stream in 32-bit by one kernel.
+    A layer without a feed-forward (``layer.feed_forward is None``) adds the mixer alone.
 
-__all__ = ["PreNormResidualBlock"]
+    In the ``(h, residual)`` pair that runs through the blocks this block returns ``(Summed, stream)``."""
+
+    def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
+        self.mixer_norm = NORMS.build(layer.norms["mixer_norm"], dtype=dtype, device=device)
+        self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(layer.norms["feed_forward_norm"], dtype=dtype, device=device)
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                     if p is not None)
+
+    graph_safe = PreNormResidualBlock.graph_safe
+    weight_slots = PreNormResidualBlock.weight_slots
+    ignorable_tensor_names = PreNormResidualBlock.ignorable_tensor_names
+    finalize_weights = PreNormResidualBlock.finalize_weights
+
+    def forward(self, h, residual, ctx, cache):
+        if residual is None:                       # the embedded tokens start the stream
+            stream = K.stream_add(h)
+        else:
+            stream = residual if residual.dtype == torch.float32 else K.stream_add(residual)
+            if not isinstance(h, Summed):          # a block in front left its last output unsummed
+                stream = K.stream_add(stream, h)
+        a = self.mixer.forward(self.mixer_norm.forward(stream), ctx, cache)
+        f = None
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(self.feed_forward_norm.forward(stream), ctx)
+        return Summed(None), K.stream_add(stream, a, f)
+
+
+BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("parallel_residual", ParallelResidualBlock)
+
+__all__ = ["ParallelResidualBlock", "PreNormResidualBlock"]

@@ -16,14 +16,16 @@ from .base import EMBEDDINGS, LM_HEADS, Part, WeightSlot
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, *, vocab_size: int, hidden_size: int, name: str, dtype, device) -> None:
+    def __init__(self, *, vocab_size: int, hidden_size: int, name: str, tensor: str | None = None,
+                 dtype, device) -> None:
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.name = name
+        self.tensor = tensor or f"{name}.weight"     # the table's full checkpoint name
         self.weight = torch.empty(self.vocab_size, self.hidden_size, dtype=dtype, device=device)
 
     def weight_slots(self) -> list[WeightSlot]:
-        return [WeightSlot(f"{self.name}.weight", self.weight)]
+        return [WeightSlot(self.tensor, self.weight)]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return K.gather_rows(self.weight, token_ids)

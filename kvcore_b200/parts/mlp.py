@@ -14,6 +14,13 @@ from .. import kernels as K
 from .base import FEED_FORWARDS, FeedForward, Summed, WeightSlot
 
 
+# suffixes of a gated feed-forward's tensors behind its name; ``tensor_names`` of a part overrides them
+GATED_TENSOR_NAMES = {
+    "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight",
+    "gate_bias": "gate_proj.bias", "up_bias": "up_proj.bias", "down_bias": "down_proj.bias",
+}
+
+
 class SwiGLU(FeedForward):
     graph_safe = True
 
@@ -24,12 +31,15 @@ class SwiGLU(FeedForward):
         intermediate_size: int,
         name: str,
         bias: bool = False,
+        tensor_names: dict | None = None,
         dtype: torch.dtype,
         device: torch.device,
     ) -> None:
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.name = name
+        self.tensor_names = dict(GATED_TENSOR_NAMES)
+        self.tensor_names.update(tensor_names or {})
         inter = self.intermediate_size
         self.group = 8 if inter % 8 == 0 else 0      # run length of the gate/up interleave (0: halves)
         self.gate_up_weight = torch.empty(2 * inter, self.hidden_size, dtype=dtype, device=device)
@@ -48,17 +58,18 @@ class SwiGLU(FeedForward):
     def weight_slots(self) -> list[WeightSlot]:
         inter, hidden = self.intermediate_size, self.hidden_size
         gate, up = self._halves(self.gate_up_weight)
+        names = {key: f"{self.name}.{suffix}" for key, suffix in self.tensor_names.items()}
         slots = [
-            WeightSlot(f"{self.name}.gate_proj.weight", gate, file_shape=(inter, hidden)),
-            WeightSlot(f"{self.name}.up_proj.weight", up, file_shape=(inter, hidden)),
-            WeightSlot(f"{self.name}.down_proj.weight", self.down_weight),
+            WeightSlot(names["gate"], gate, file_shape=(inter, hidden)),
+            WeightSlot(names["up"], up, file_shape=(inter, hidden)),
+            WeightSlot(names["down"], self.down_weight),
         ]
         if self.gate_up_bias is not None:
             gate_bias, up_bias = self._halves(self.gate_up_bias)
             slots += [
-                WeightSlot(f"{self.name}.gate_proj.bias", gate_bias, init="normal", file_shape=(inter,)),
-                WeightSlot(f"{self.name}.up_proj.bias", up_bias, init="normal", file_shape=(inter,)),
-                WeightSlot(f"{self.name}.down_proj.bias", self.down_bias, init="normal"),
+                WeightSlot(names["gate_bias"], gate_bias, init="normal", file_shape=(inter,)),
+                WeightSlot(names["up_bias"], up_bias, init="normal", file_shape=(inter,)),
+                WeightSlot(names["down_bias"], self.down_bias, init="normal"),
             ]
         return slots
 
@@ -79,6 +90,40 @@ class SwiGLU(FeedForward):
         return (Summed(sumsq) if pending is None else pending), residual
 
 
-FEED_FORWARDS.register("swiglu", SwiGLU)
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with bounded branches: ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``,
+    ``down(g * sigmoid(alpha * g) * (u + shift))``.  Gate and up are the two halves of one matrix; no biases."""
 
-__all__ = ["SwiGLU"]
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 shift: float = 1.0, name: str, tensor_names: dict | None = None,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        if not self.limit > 0:
+            raise ValueError(f"the clamp limit must be positive, got {limit}")
+        self.name = name
+        self.tensor_names = dict(GATED_TENSOR_NAMES)
+        self.tensor_names.update(tensor_names or {})
+        self.gate_up_weight = torch.empty(2 * self.intermediate_size, self.hidden_size, dtype=dtype, device=device)
+        self.down_weight = torch.empty(self.hidden_size, self.intermediate_size, dtype=dtype, device=device)
+
+    def weight_slots(self) -> list[WeightSlot]:
+        inter = self.intermediate_size
+        return [
+            WeightSlot(f"{self.name}.{self.tensor_names['gate']}", self.gate_up_weight[:inter]),
+            WeightSlot(f"{self.name}.{self.tensor_names['up']}", self.gate_up_weight[inter:]),
+            WeightSlot(f"{self.name}.{self.tensor_names['down']}", self.down_weight),
+        ]
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        hidden = K.glu_clamped(K.linear(x, self.gate_up_weight), alpha=self.alpha, limit=self.limit, shift=self.shift)
+        return K.linear(hidden, self.down_weight)
+
+
+FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("clamped_glu", ClampedGLU)
+
+__all__ = ["ClampedGLU", "GATED_TENSOR_NAMES", "SwiGLU"]

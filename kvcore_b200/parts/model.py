@@ -13,7 +13,7 @@ import torch
 
 from .. import kernels as K
 from ..config.model_spec import ModelSpec
-from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (register the stock parts)
+from . import attention, block, embedding, mlp, moe, norm, rope  # noqa: F401  (register the stock parts)
 from .base import BLOCKS, EMBEDDINGS, LM_HEADS, NORMS, CacheSpec, StateSpec, Summed, WeightSlot
 
 

@@ -1,4 +1,4 @@
-"""RMS normalisation with the residual sum folded in.
+"""RMS normalisation with the residual sum folded in, and layer normalisation over a 32-bit stream.
 
 Formula as the reference computes it (kvcore/model/layer/rmsnorm.py:19-26): the optional
 residual is added first and becomes the new residual; then in 32-bit
@@ -39,6 +39,41 @@ class RMSNorm(Norm):
         return self.weight, self.eps
 
 
-NORMS.register("rmsnorm", RMSNorm)
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` with the biased variance, statistics in 32-bit.
 
-__all__ = ["RMSNorm"]
+    It reads rows of the activation type or of a 32-bit residual stream and writes the activation type, so a
+    block that keeps its stream in 32-bit normalises it without a copy.  ``tensor`` is the weight's full
+    checkpoint name (default ``<name>.weight``); ``bias`` adds ``<name>.bias`` (or ``bias_tensor``)."""
+
+    graph_safe = True
+
+    def __init__(self, *, size: int, eps: float, name: str, tensor: str | None = None, bias: bool = False,
+                 bias_tensor: str | None = None, dtype: torch.dtype, device: torch.device):
+        self.size = int(size)
+        self.eps = float(eps)
+        self.name = name
+        self.dtype = dtype
+        self.tensor = tensor or f"{name}.weight"
+        self.bias_tensor = bias_tensor or f"{name}.bias"
+        self.weight = torch.empty(self.size, dtype=dtype, device=device)
+        self.bias = torch.empty(self.size, dtype=dtype, device=device) if bias else None
+
+    def weight_slots(self) -> list[WeightSlot]:
+        slots = [WeightSlot(self.tensor, self.weight, init="ones")]
+        if self.bias is not None:
+            slots.append(WeightSlot(self.bias_tensor, self.bias, init="zeros"))
+        return slots
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return K.layer_norm(x, self.weight, self.bias, self.eps, out_dtype=self.dtype)
+
+    def forward_residual(self, h: torch.Tensor, residual: torch.Tensor):
+        residual = K.stream_add(residual, h) if residual.dtype == torch.float32 else residual.add_(h)
+        return self.forward(residual), residual
+
+
+NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("layernorm", LayerNorm)
+
+__all__ = ["LayerNorm", "RMSNorm"]

@@ -67,14 +67,21 @@ class RotaryEncoding(PositionEncoding):
         low_freq_factor: float = 1.0,
         high_freq_factor: float = 4.0,
         original_max_position_embeddings: int = 8192,
+        rotary_dim: int | None = None,
         name: str | None = None,
         dtype: torch.dtype,
         device: torch.device,
     ) -> None:
         self.name = name
-        if head_dim % 2:
-            raise ValueError(f"rotary encoding needs an even head_dim, got {head_dim}")
-        self.head_dim = int(head_dim)
+        # ``rotary_dim``: only the first that many entries of a head turn (entry i with entry
+        # i + rotary_dim/2, frequencies theta^(-2i/rotary_dim)); the rest of the head passes unchanged
+        self.rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
+        if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= head_dim:
+            raise ValueError(f"rotary encoding needs an even number of turned entries within the head, "
+                             f"got {self.rotary_dim} of {head_dim}")
+        self.head_dim, head_dim = int(head_dim), self.rotary_dim
+        if head_dim == 0:
+            raise ValueError("a rotary encoding that turns nothing: leave the position encoding out instead")
         # layers with the same frequency parameters share one cos/sin table per step
         self.table_key = ("rope", int(head_dim), float(theta), str(rope_type), float(factor),
                           float(low_freq_factor), float(high_freq_factor), int(original_max_position_embeddings))
@@ -90,10 +97,12 @@ class RotaryEncoding(PositionEncoding):
         return [] if self.name is None else [f"{self.name}.inv_freq"]
 
     def cos_sin(self, ctx) -> torch.Tensor:
-        """``[T, D/2, 2]`` (cos, sin) of this step's positions; one table per step and frequency table."""
+        """``[T, rotary_dim/2, 2]`` (cos, sin) of this step's positions; one table per step and frequency table."""
         return ctx.shared(self.table_key, lambda: K.rope_table(ctx.positions, self.inv_freq))
 
     def apply(self, q: torch.Tensor, k: torch.Tensor | None, ctx) -> None:
+        if self.rotary_dim != self.head_dim:
+            raise NotImplementedError("a rotation of part of the head is applied through its cos/sin table")
         K.rope_inplace(q, k, ctx.positions, self.inv_freq)
 
 

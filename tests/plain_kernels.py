@@ -117,16 +117,16 @@ def rope_kv_write(qkv, positions, req_index, cos_sin, table, k_cache, v_cache,
 
 def paged_attention(qkv, k_cache, v_cache, table, ctx, num_heads, num_kv_heads, head_dim, scale, window,
                     *, force_general=False, num_splits=None, use_tma=True, use_tc5=True, cos_sin=None,
-                    write_kv=None):
+                    write_kv=None, keep_first=0):
     if write_kv is not None:   # the call also rotates q, k and writes this step's k, v
         rope_kv_write(qkv, ctx.positions, ctx.req_index, cos_sin, table, k_cache, v_cache,
                       num_heads, num_kv_heads, head_dim, write_kv=write_kv)
     return paged_attention_plain(qkv, k_cache, v_cache, table, ctx.positions, ctx.req_index,
-                                 num_heads, num_kv_heads, head_dim, scale, window)
+                                 num_heads, num_kv_heads, head_dim, scale, window, keep_first)
 
 
 def paged_attention_plain(qkv, k_cache, v_cache, table, positions, req_index,
-                          num_heads, num_kv_heads, head_dim, scale, window):
+                          num_heads, num_kv_heads, head_dim, scale, window, keep_first=0):
     tokens = qkv.shape[0]
     page_size = k_cache.shape[2]
     group = num_heads // num_kv_heads
@@ -136,6 +136,8 @@ def paged_attention_plain(qkv, k_cache, v_cache, table, positions, req_index,
         pos = int(positions[t])
         first = 0 if not window else max(0, pos - window + 1)
         keys = torch.arange(first, pos + 1, device=qkv.device)
+        if keep_first and first > 0:     # the kept first positions that lie behind the window
+            keys = torch.cat((torch.arange(0, min(keep_first, first), device=qkv.device), keys))
         pages = table[int(req_index[t])].long()[keys // page_size]
         assert bool((pages > 0).all()), "read through the null page"
         offsets = keys % page_size
@@ -147,6 +149,111 @@ def paged_attention_plain(qkv, k_cache, v_cache, table, positions, req_index,
             probs = torch.softmax(scores, dim=0)
             out[t, h * head_dim:(h + 1) * head_dim] = (probs @ v[:, g, :]).to(qkv.dtype)
     return out
+
+
+def layer_norm(x, weight, bias, eps, out_dtype=None):
+    xf = x.float()
+    centred = xf - xf.mean(-1, keepdim=True)
+    y = centred / torch.sqrt(centred.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype or x.dtype)
+
+
+def stream_add(base, a=None, b=None):
+    out = base if base.dtype == torch.float32 else base.float()
+    if a is not None:
+        addend = a.float() if b is None else a.float() + b.float()
+        out = out.add_(addend) if out is base else out + addend
+    return out
+
+
+def qk_prepare(rows, positions, req_index, cos_sin, table, k_cache, v_cache, num_heads, num_kv_heads, head_dim, *,
+               rotary_dim=None, norm=None, q_norm_weight=None, k_norm_weight=None, eps=0.0, value_from_key=False,
+               write_kv=True):
+    tokens = rows.shape[0]
+    q_size, kv_size = num_heads * head_dim, num_kv_heads * head_dim
+    q, k = rows[:, :q_size].float(), rows[:, q_size:q_size + kv_size].float()
+    v = (rows[:, q_size:q_size + kv_size] if value_from_key else rows[:, q_size + kv_size:]).clone()
+
+    def rms(x, weight, heads):
+        if norm is None:
+            return x
+        shaped = x if norm == "projection" else x.view(tokens, heads, head_dim)
+        shaped = shaped * torch.rsqrt(shaped.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+        return shaped.reshape(tokens, -1)
+
+    def turn(x, heads):
+        x = x.view(tokens, heads, head_dim)
+        if cos_sin is None:
+            return x
+        rot = head_dim if rotary_dim is None else rotary_dim
+        half = rot // 2
+        cos, sin = cos_sin[:, None, :, 0], cos_sin[:, None, :, 1]
+        a, b = x[..., :half], x[..., half:rot]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., rot:]), dim=-1)
+
+    q = turn(rms(q, q_norm_weight, num_heads), num_heads).to(rows.dtype)
+    k = turn(rms(k, k_norm_weight, num_kv_heads), num_kv_heads).to(rows.dtype)
+    rows[:, :q_size] = q.reshape(tokens, q_size)
+    rows[:, q_size:q_size + kv_size] = k.reshape(tokens, kv_size)
+    if write_kv:
+        page_size = k_cache.shape[2]
+        for t in range(tokens):
+            pos = int(positions[t])
+            page = int(table[int(req_index[t]), pos // page_size])
+            assert page > 0, "write through the null page"
+            k_cache[page, :, pos % page_size, :] = k[t]
+            v_cache[page, :, pos % page_size, :] = v[t].view(num_kv_heads, head_dim)
+
+
+def glu_clamped(gate_up, *, alpha, limit, shift):
+    inter = gate_up.shape[1] // 2
+    g = gate_up[:, :inter].float().clamp(max=limit)
+    u = gate_up[:, inter:].float().clamp(min=-limit, max=limit)
+    return (g * torch.sigmoid(alpha * g) * (u + shift)).to(gate_up.dtype)
+
+
+def moe_route(x, router, top, *, score="sigmoid", renormalize=False, gate_rows=None):
+    z = x.float() @ router.float().T
+    scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
+    ids = torch.empty(x.shape[0], top, dtype=torch.int32, device=x.device)
+    weights = torch.empty(x.shape[0], top, dtype=torch.float32, device=x.device)
+    left = scores.clone()
+    for slot in range(top):          # the largest, the lowest index among equals
+        best = left.max(dim=-1, keepdim=True).values
+        index = (left == best).float().argmax(dim=-1)
+        ids[:, slot] = index
+        weights[:, slot] = best[:, 0]
+        left[torch.arange(x.shape[0]), index] = -float("inf")
+    if renormalize:
+        weights = weights / weights.sum(-1, keepdim=True)
+    gates = None if gate_rows is None else torch.sigmoid(x.float() @ gate_rows.float().T)
+    return ids, weights, gates
+
+
+def moe_experts(x, ids, weights, gate_up, down, *, weight_on_input):
+    tokens, top = ids.shape
+    ff = gate_up.shape[1] // 2
+    out = torch.empty(tokens * top, down.shape[1], dtype=x.dtype, device=x.device)
+    for t in range(tokens):
+        for s in range(top):
+            e, w = int(ids[t, s]), weights[t, s]
+            a = (w * x[t].float()).to(x.dtype).float() if weight_on_input else x[t].float()
+            g = (gate_up[e, :ff].float() @ a).to(x.dtype).float()
+            u = (gate_up[e, ff:].float() @ a).to(x.dtype).float()
+            hidden = ((g * torch.sigmoid(g)).to(x.dtype).float() * u).to(x.dtype).float()
+            if not weight_on_input:
+                hidden = (w * hidden).to(x.dtype).float()
+            out[t * top + s] = (down[e].float() @ hidden).to(x.dtype)
+    return out
+
+
+def moe_combine(expert_out, tokens, top, shared=None, gates=None):
+    y = expert_out.float().view(tokens, top, -1).sum(1)
+    if shared is not None:
+        y = y + (shared.float() if gates is None else gates[:, :1] * shared.float())
+    return y.to(expert_out.dtype)
 
 
 def linear(x, weight, bias=None, *, out_dtype=None):
@@ -231,6 +338,7 @@ def sample(logits, packed_params, eps):
 _NAMES = [
     "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "feed_tokens", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
+    "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine",
 ]
 
 

@@ -108,7 +108,7 @@ extern "C" int kvb_moe_route(int* ids_out, float* weights_out, float* gate_out, 
   return 0;
 }
 
-// sorted [capacity] (capacity = a multiple of MOE_BM covering pairs + experts * (MOE_BM - 1)),
+// sorted [capacity] (capacity = MOE_BM * min(pairs, ceil((pairs + experts * (MOE_BM - 1)) / MOE_BM))),
 // tile_expert [capacity / MOE_BM], meta[0] = tiles used.
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ meta,
@@ -148,7 +148,9 @@ extern "C" int kvb_moe_align(int* sorted, int* tile_expert, int* meta, const int
                              int capacity, cudaStream_t stream) {
   if (pairs == 0) return 0;
   KVB_REQUIRE(E > 0 && E <= 8192, "moe_align: between 1 and 8192 experts");
-  KVB_REQUIRE(capacity % MOE_BM == 0 && capacity >= pairs + (long long)E * (MOE_BM - 1) - (MOE_BM - 1),
+  // tiles used: one per started run of MOE_BM pairs of an expert, so at most one per pair
+  const long long padded = (pairs + (long long)E * (MOE_BM - 1) + MOE_BM - 1) / MOE_BM;
+  KVB_REQUIRE(capacity % MOE_BM == 0 && capacity / MOE_BM >= (padded < pairs ? padded : pairs),
               "moe_align: the sorted list is too short");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "moe_align: no status word");

@@ -49,6 +49,7 @@ struct DecodeParams {
   float* partial_o;   // [reqs, KVH, splits, 16, D]
   float* partial_ml;  // [reqs, KVH, splits, 16, 2]
   int* status;
+  float* lse;                // optional [tokens, H]: log2 of the sum of 2^(scaled score) over the keys seen (-inf: none)
   // Rotation and cache write of this step's tokens done here instead of in a kernel in front
   // cos_sin != null: q rows are rotated on their way into shared memory.  k_cache != null: the
   // block whose key range holds a new token rotates its key (if cos_sin), writes key and value into
@@ -563,6 +564,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         }
         if (p.num_splits == 1) {
           const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+          if (p.lse != nullptr && d == 0)
+            p.lse[(size_t)token * p.H + head] = total > 0.0f ? m + log2f(total) : -INFINITY;
           if (!(total > 0.0f)) { acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f); total = 1.0f; }
           __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x / total, acc.y / total), hi = __floats2bfloat162_rn(acc.z / total, acc.w / total);
           uint2 packed;
@@ -629,6 +632,8 @@ __global__ void flash_decode_combine_kernel(const DecodeParams p) {
   const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
   p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
       __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+  if (p.lse != nullptr && d == 0)
+    p.lse[(size_t)token * p.H + head] = total > 0.0f ? m + log2f(total) : -INFINITY;
 }
 
 // ---- host side -----------------------------------------------------------------------------
@@ -687,7 +692,7 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
                                     int num_pages, float scale, int window, int num_splits, float* scratch,
                                     const float* cos_sin, void* k_cache, void* v_cache, int* work, int max_blocks,
-                                    cudaStream_t stream) {
+                                    float* lse, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == 64 || D == 128, "decode attention (TMA): head_dim must be 64 or 128");
   KVB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "decode attention (TMA): give both caches or none");
@@ -714,6 +719,7 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   p.partial_o = scratch;
   p.partial_ml = scratch ? scratch + (size_t)num_reqs * KVH * p.num_splits * 16 * D : nullptr;
   p.status = kvb_status_word();
+  p.lse = lse;
   KVB_REQUIRE(p.status != nullptr, "decode attention (TMA): no status word");
   // q points at the qkv rows [q heads | k heads | v heads]
   p.cos_sin = (const float2*)cos_sin;

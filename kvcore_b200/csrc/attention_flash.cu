@@ -37,6 +37,7 @@ struct FlashParams {
   float* partial_o;          // [reqs, KVH, splits, 16, D]
   float* partial_ml;         // [reqs, KVH, splits, 16, 2]
   int* status;
+  float* lse;                // optional [tokens, H]: log2 of the sum of 2^(scaled score) over the keys seen (-inf: none)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -330,6 +331,8 @@ flash_paged_kernel(const FlashParams p) {
 #pragma unroll
       for (int j = 0; j < DBLOCKS; ++j)
         *reinterpret_cast<unsigned*>(dst + j * 8) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+      if (p.lse != nullptr && (lane & 3) == 0)
+        p.lse[(size_t)token * p.H + head] = row_sum[h] > 0.0f ? row_max[h] + log2f(row_sum[h]) : -INFINITY;
     }
     return;
   }
@@ -372,6 +375,8 @@ flash_paged_kernel(const FlashParams p) {
       const int head = kvh * p.G + r % p.G;
       p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
           __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+      if (p.lse != nullptr && d == 0)
+        p.lse[(size_t)token * p.H + head] = total > 0.0f ? m + log2f(total) : -INFINITY;
     } else {
       const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
       p.partial_o[(slot * 16 + r) * D + d] = acc;
@@ -430,6 +435,8 @@ __global__ void flash_combine_kernel(const FlashParams p) {
   const int head = kvh * p.G + r % p.G;
   p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
       __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+  if (p.lse != nullptr && d == 0)
+    p.lse[(size_t)token * p.H + head] = total > 0.0f ? m + log2f(total) : -INFINITY;
 }
 
 template <int D>
@@ -485,7 +492,7 @@ extern "C" int kvb_flash_paged_attention(void* out, long long out_stride, const 
                                          const int* context_lens, int num_reqs, int max_query_len,
                                          int H, int KVH, int D, int page_size, int num_pages,
                                          float scale, int window, int num_splits, float* scratch,
-                                         cudaStream_t stream) {
+                                         float* lse, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D % 16 == 0 && D >= 16 && D <= 128, "flash attention: head_dim must be a multiple of 16 up to 128");
   KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "flash attention: H must be a multiple of KVH");
@@ -503,6 +510,7 @@ extern "C" int kvb_flash_paged_attention(void* out, long long out_stride, const 
   p.page_size = page_size; p.num_pages = num_pages; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = kvb_status_word();
+  p.lse = lse;
   KVB_REQUIRE(p.status != nullptr, "flash attention: no status word");
   const int max_rows = max_query_len * p.G;
   const bool split_mode = max_rows <= 16;
@@ -596,6 +604,7 @@ extern "C" int kvb_flash_paged_attention_static(void* out, long long out_stride,
   p.page_size = page_size; p.num_pages = num_pages; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.lse = nullptr;
   p.num_splits = splits;
   p.partial_o = scratch;
   p.partial_ml = scratch + (size_t)num_reqs * KVH * splits * 16 * D;

@@ -59,6 +59,7 @@ struct Tc5Params {
   int num_reqs, H, KVH, G, page_size, num_pages, window;
   float scale_log2;
   int* status;
+  float* lse;                // optional [tokens, H]: log2 of the sum of 2^(scaled score) over the keys seen (-inf: none)
   int q_by_tma;                // the query tiles are brought by TMA (q_map is valid)
 };
 
@@ -468,6 +469,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
 #pragma unroll
       for (int c = 0; c < 4; ++c) kvb_tc5_ld32(o_addr + c * 32, o[c]);
       kvb_tc5_wait_ld();
+      if (row_valid && p.lse != nullptr)   // the row sum carries the factor 2^T5_ROUND_SHIFT
+        p.lse[(size_t)(q_begin + flat / p.G) * p.H + kvh * p.G + flat % p.G] =
+            row_sum > 0.0f ? row_max + log2f(row_sum) - T5_ROUND_SHIFT : -INFINITY;
       if (row_valid) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -530,7 +534,8 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
                                      const void* k_map_host, const void* v_map_host, const int* table,
                                      int table_stride, const int* query_start, const int* context_lens,
                                      int num_reqs, int max_query_len, int num_tokens, int H, int KVH, int D,
-                                     int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
+                                     int page_size, int num_pages, float scale, int window, float* lse,
+                                     cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == T5_D, "prefill attention (tcgen05): head_dim must be 128");
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
@@ -549,6 +554,7 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   p.page_size = page_size; p.num_pages = num_pages; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = kvb_status_word();
+  p.lse = lse;
   KVB_REQUIRE(p.status != nullptr, "prefill attention (tcgen05): no status word");
   alignas(64) CUtensorMap k_map, v_map, q_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));

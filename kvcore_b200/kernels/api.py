@@ -56,13 +56,15 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_moe_gemm": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
         "kvb_moe_combine": [_vp, _vp, _int, _int, _vp, _vp, _int, _int, _int, _vp],
         "kvb_flash_paged_attention": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int,
-                                      _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
+                                      _int, _int, _int, _int, _float, _int, _int, _vp, _vp, _vp],
+        "kvb_kept_first_merge": [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
+                                 _int, _int, _float, _int, _int, _int, _vp],
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
-                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp],
+                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp],
         "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int, _int,
-                                  _int, _int, _int, _float, _int, _vp],
+                                  _int, _int, _int, _float, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _int, _vp],
@@ -511,10 +513,21 @@ def paged_attention(
     if keep_first < 0 or (keep_first and not window):
         raise KernelError(f"kept first positions ({keep_first}) need a window")
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    if (not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0
-            and not keep_first):
+    if not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0:
         group = num_heads // num_kv_heads
         geometry = (num_heads, num_kv_heads, head_dim, float(scale), int(window or 0))
+        # Kept first positions: the windowed kernels also leave each row's log-sum, and a small kernel
+        # behind them adds the kept keys that lie behind the row's window.
+        lse = (torch.empty((tokens, num_heads), dtype=torch.float32, device=qkv.device)
+               if keep_first and write_kv is None else None)
+
+        def add_kept_first() -> None:
+            if lse is not None:
+                _call("kvb_kept_first_merge", out.data_ptr(), out.stride(0), lse.data_ptr(), qkv.data_ptr(),
+                      qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
+                      ctx.positions.data_ptr(), ctx.req_index.data_ptr(), tokens, num_heads, num_kv_heads, head_dim,
+                      page_size, num_pages, float(scale), int(window), int(keep_first), _dtype_code(qkv), _stream())
+
         # A mixed step (portions of prompts beside single decoded tokens) is two kinds of work: the
         # portions fill query tiles of 128 rows, a decoded token has at most 16 rows a kv head and would
         # leave such a tile almost empty while walking all its keys.  When the batch says how long each
@@ -529,10 +542,12 @@ def paged_attention(
                 for begin, end in ((0, long_count), (long_count, ctx.num_reqs)):
                     part = _RequestRun(ctx, begin, end)
                     _flash_attention_into(out, qkv, k_cache, v_cache, table[begin:end], part, geometry,
-                                          None, use_tma, use_tc5, None, None)
+                                          None, use_tma, use_tc5, None, None, lse)
+                add_kept_first()
                 return out
         _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_splits, use_tma, use_tc5,
-                              cos_sin, write_kv)
+                              cos_sin, write_kv, lse)
+        add_kept_first()
         return out
     _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
@@ -558,12 +573,13 @@ class _RequestRun:
 
 
 def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_splits, use_tma, use_tc5,
-                          cos_sin, write_kv) -> None:
+                          cos_sin, write_kv, lse=None) -> None:
     """The tensor-core attention kernels on one batch (or one run of requests of a batch): the TMA
     decode kernel for at most 16 rows a kv head, the tcgen05 kernel for portions of prompts, the
     ``mma.sync`` kernel for the shapes those two do not take."""
     num_heads, num_kv_heads, head_dim, scale, window = geometry
     num_pages, _, page_size, _ = k_cache.shape
+    lse_ptr = None if lse is None else lse.data_ptr()    # [tokens, H] rows of the whole step, as ``out``
     group = num_heads // num_kv_heads
     split_mode = ctx.max_query_len * group <= 16
     bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
@@ -583,7 +599,7 @@ def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_
               None if cos_sin is None else cos_sin.data_ptr(),
               k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None,
               _decode_work(qkv.device).data_ptr() if TMA_DECODE_SHARED_WORK else None,
-              sms * TMA_DECODE_BLOCKS_PER_SM, _stream(),
+              sms * TMA_DECODE_BLOCKS_PER_SM, lse_ptr, _stream(),
               kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
         return
     if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
@@ -593,7 +609,7 @@ def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_
               ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
               ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
               qkv.shape[0], num_heads, num_kv_heads, head_dim, page_size, num_pages, scale, window,
-              _stream())
+              lse_ptr, _stream())
         return
     splits = 1
     if split_mode:
@@ -606,7 +622,8 @@ def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
           ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
           num_heads, num_kv_heads, head_dim, page_size, num_pages, scale, window,
-          splits, None if scratch is None else scratch.data_ptr(), _stream(), kernels=2 if splits > 1 else 1)
+          splits, None if scratch is None else scratch.data_ptr(), lse_ptr, _stream(),
+          kernels=2 if splits > 1 else 1)
 
 
 _mm_out_dtype_ok: bool | None = None
@@ -619,12 +636,12 @@ STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 _stream_scratch: dict[int, torch.Tensor] = {}
 
 
-TRACE_TAGS = {17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+TRACE_TAGS = {25: "kept_first_merge", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
-                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe")
+                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe", "attention_kept_first")
 _trace_buffer: torch.Tensor | None = None
 
 

@@ -28,14 +28,16 @@ from .step import StepEntry, StepFunction
 
 
 def build_replay(model_dir: str, dtype: str, max_tokens: int, *, page_size: int = 16,
-                 max_live: int = 8, device: str = "cuda:0", fill_freed_pages: str | None = None):
+                 max_live: int = 8, device: str = "cuda:0", fill_freed_pages: str | None = None,
+                 max_model_len: int | None = None):
     """The model with a cache pool for ``max_tokens`` tokens, wired by the model runner as for
-    generation; returns (step function, kv manager)."""
+    generation; returns (step function, kv manager).  ``max_model_len`` (default ``max_tokens``): the
+    longest request; a model whose layers all see a window may run requests longer than its pool."""
     if max_tokens <= 0:
         raise ValueError(f"--max-tokens must be positive, got {max_tokens}")
     pages = -(-max_tokens // page_size) + 1  # + the null page
     config = KVCoreConfig(
-        model_config=ModelConfig(model=model_dir, dtype=dtype, max_model_len=max_tokens),
+        model_config=ModelConfig(model=model_dir, dtype=dtype, max_model_len=max_model_len or max_tokens),
         cache_config=CacheConfig(block_size=page_size, num_gpu_blocks=pages,
                                  debug_fill_freed_pages=fill_freed_pages),
         scheduler_config=SchedulerConfig(max_num_seqs=max_live, max_num_scheduled_tokens=max_tokens),

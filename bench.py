@@ -132,14 +132,18 @@ def model_numbers(config: dict, layers: int) -> dict:
     )
 
 
-def build_runner(shape: dict, layers: int, max_seqs: int, max_len: int, num_pages: int, max_tokens: int):
+def build_runner(shape: dict, layers: int, max_seqs: int, max_len: int, num_pages: int, max_tokens: int,
+                 raw_config: dict | None = None):
+    """``raw_config``: a whole config.json (any registered architecture) instead of a Llama shape cut to ``layers``."""
     import torch
 
     from kvcore_b200 import CacheConfig, DeviceConfig, KVCoreConfig, LoadConfig, ModelConfig, SchedulerConfig
     from kvcore_b200.engine.runner import ModelRunner
 
     folder = Path(tempfile.mkdtemp(prefix="kvcore_bench_"))
-    (folder / "config.json").write_text(json.dumps({k: v for k, v in dict(shape, num_hidden_layers=layers).items() if v is not None}))
+    (folder / "config.json").write_text(json.dumps(
+        raw_config if raw_config is not None
+        else {k: v for k, v in dict(shape, num_hidden_layers=layers).items() if v is not None}))
     config = KVCoreConfig(
         model_config=ModelConfig(model=str(folder), dtype="bfloat16", max_model_len=max_len),
         load_config=LoadConfig(random_weights=True, seed=0),
@@ -595,6 +599,129 @@ def _run_reference(args, ref: Path) -> dict:
     }
 
 
+# ---- two designs at equal layer sizes ("--designs") ----------------------------------------------------
+# name -> width, heads, kv heads, head size, feed-forward width of the dense layers, experts, chosen, expert width,
+# shared expert width (chosen * expert width + shared width = the dense width: equal work per token), vocabulary
+DESIGN_SIZES = {
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, experts=32, top=4, expert_ff=1792,
+                  shared_ff=7168, vocab=128256),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, experts=16, top=2, expert_ff=2048,
+                  shared_ff=4096, vocab=32000),
+}
+DESIGN_LAYERS = 4
+
+
+def toposun_config(size: dict, feed_forward: str, window: int, keep_first: int) -> dict:
+    """A Toposun config.json of ``DESIGN_LAYERS`` layers: ``feed_forward`` "dense" or "moe"."""
+    if feed_forward == "dense":
+        mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    else:
+        mlp = {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"]},
+               "expert": {"ff": size["expert_ff"]}, "shared": {"ff": size["shared_ff"]}}
+    layer = {"type": "attention", "mlp": mlp,
+             "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+                       "scale": size["dim"] ** -0.5, "rot": {"base": 10000.0, "dims": size["dim"] // 2},
+                       "mask": {"size": window, "keep_first": keep_first}}}
+    return {"architecture": "Toposun", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+            "layers": [layer] * DESIGN_LAYERS}
+
+
+def llama_config(size: dict) -> dict:
+    return dict(LLAMA_31_8B, hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=DESIGN_LAYERS,
+                num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
+                vocab_size=size["vocab"], tie_word_embeddings=True)
+
+
+def kernel_times(events: list[dict]) -> dict:
+    """Microseconds and launches per kernel of this library from a timeline trace: a launch runs from its
+    first block's return from the wait for the kernel in front to its last block's exit."""
+    out: dict[str, list] = {}
+    firsts: dict[str, list] = {}
+    lasts: dict[str, list] = {}
+    for event in events:                      # sorted by entry; blocks of one launch may enter in any order
+        if event["block"] == "first":
+            firsts.setdefault(event["kernel"], []).append(event)
+        elif event["block"] == "last":
+            lasts.setdefault(event["kernel"], []).append(event)
+    for name, first_blocks in firsts.items():
+        last_blocks = lasts.get(name, [])
+        total = 0.0
+        for index, first in enumerate(first_blocks):
+            # the i-th launch of a kernel: its first and its last block (a one-block launch has only the first)
+            last = last_blocks[index] if len(last_blocks) == len(first_blocks) else first
+            total += (max(first["exit"], last["exit"]) - min(first["waited"], last["waited"])) / 1000.0
+        out[name] = [total, len(first_blocks)]
+    return {name: {"us": round(us, 1), "launches": count} for name, (us, count) in sorted(out.items())}
+
+
+def compare_designs(args) -> int:
+    """Prefill (2,048 tokens) and decode (batch 8 and 64 at 2,048 tokens of context) of Toposun, dense and
+    mixture feed-forward, beside a Llama of the same width, heads and feed-forward work, a few layers each;
+    and where one step's time goes, kernel by kernel."""
+    import torch
+
+    import kvcore_b200.kernels as K
+    from kvcore_b200.engine.step import StepEntry
+
+    context, batches = 2048, (8, 64)
+    max_len = context + PREFILL_TOKENS + args.steps + args.warmup + 8
+    pages = max(batches) * (-(-max_len // BLOCK_SIZE)) + 1
+    results = []
+    peaks = measured_peaks()
+    for size_name in ([args.design_size] if args.design_size else list(DESIGN_SIZES)):
+        size = DESIGN_SIZES[size_name]
+        models = {
+            "llama": llama_config(size),
+            "toposun_dense_full_window": toposun_config(size, "dense", 1 << 20, 0),
+            "toposun_dense": toposun_config(size, "dense", 1024, 4),
+            "toposun_moe": toposun_config(size, "moe", 1024, 4),
+        }
+        for model_name, raw in models.items():
+            config, runner = build_runner({}, DESIGN_LAYERS, max(batches), max_len, pages,
+                                          max(PREFILL_TOKENS, max(batches)), raw_config=raw)
+            row = {"size": size_name, "model": model_name, "layers": DESIGN_LAYERS,
+                   "weight_gb": round(runner.model.weight_bytes() / 1e9, 2)}
+            ms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+            row["prefill_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+            row["prefill_ms"] = round(ms, 3)
+            for batch in batches:
+                ms = time_decode(runner, batch, context, args.steps, args.warmup)
+                row[f"decode_b{batch}_tokens_per_s"] = round(batch * 1000.0 / ms, 1)
+                row[f"decode_b{batch}_ms"] = round(ms, 4)
+            # one prefill step and one eager decode step under the kernel timeline trace
+            kv = runner.kv_manager
+            generator = torch.Generator().manual_seed(5)
+            vocab = runner.model.spec.vocab_size
+            prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=generator).tolist()
+            assert kv.allocate_slots("traced", PREFILL_TOKENS)
+            K.trace_start("cuda:0")
+            runner.step_function.step([StepEntry("traced", prompt, (PREFILL_TOKENS - 1,))])
+            row["prefill_kernels"] = kernel_times(K.trace_stop())
+            kv.free("traced")
+            ids = [f"traced-{i}" for i in range(8)]
+            for rid in ids:
+                assert kv.allocate_slots(rid, context + 1)
+                kv.advance(rid, context)
+            graphs, runner.step_function.use_cuda_graphs = runner.step_function.use_cuda_graphs, False
+            K.trace_start("cuda:0")
+            runner.step_function.step([StepEntry(rid, [1], (0,)) for rid in ids])
+            row["decode_b8_kernels"] = kernel_times(K.trace_stop())
+            runner.step_function.use_cuda_graphs = graphs
+            for rid in ids:
+                kv.free(rid)
+            status = K.read_status()
+            if status:
+                raise RuntimeError(f"a kernel reported status {status} during the measurement: the numbers are void")
+            results.append(row)
+            del runner, config
+            gc.collect()
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "prefill and decode of two designs at equal layer sizes, bf16, random weights",
+                      "impl": "ours", "context": context, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps,
+                      "warmup": args.warmup, "peaks": peaks, "results": results}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -614,7 +741,14 @@ def main() -> int:
     parser.add_argument("--serve", action="store_true",
                         help="continuous batching instead: 64 requests of 128-4,096 random prompt tokens, "
                              "512 tokens a step, 128 generated tokens each, through LLMEngine.generate")
+    parser.add_argument("--designs", action="store_true",
+                        help="instead: Toposun (dense and mixture feed-forward) beside a Llama of equal layer sizes, "
+                             "prefill and decode throughput and each kernel's share of a step; prints a line of its own")
+    parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one size of --designs")
     args = parser.parse_args()
+    if args.designs:
+        args.warmup = max(args.warmup, 3)
+        return compare_designs(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

@@ -3,8 +3,8 @@
 // A windowed attention kernel leaves, per (token, head), its normalised output and
 //   lse = log2( sum over the window's keys of 2^(score * scale * log2 e) ).
 // A query at position p with window w and `keep_first` kept positions also sees the keys
-// j < min(keep_first, p - w + 1): those behind its window.  One warp per (token, head) scores them
-// (a lane a key, 32-bit dot products in ascending order, online maximum and sum in the same base-2
+// j < min(keep_first, p - w + 1): those behind its window.  One warp per (token, head) scores them one
+// after the other (the lanes spread over the head, 32-bit, online maximum and sum in the same base-2
 // domain) and merges:
 //   out = (out_w * 2^(lse - M) + sum_j 2^(s_j - M) v_j) / (2^(lse - M) + sum_j 2^(s_j - M)),  M = max(lse, max_j s_j).
 // Rows whose window reaches back into the kept positions have nothing to add and are left as they are.
@@ -45,40 +45,26 @@ kept_first_merge_kernel(T* __restrict__ out, int out_stride, const float* __rest
   float running_max = -INFINITY, running_sum = 0.0f;
   const size_t head_off = (size_t)kvh * page_size * D;
   const size_t page_elems = (size_t)KVH * page_size * D;
-  for (int base = 0; base < kept; base += 32) {
-    const int key = base + lane;
-    float score = -INFINITY;
-    int page = 0;
-    if (key < kept) {
-      page = pages[key / page_size];
-      if (page <= 0 || page >= num_pages) {
-        atomicOr(status, KVB_STATUS_BAD_PAGE);
-        page = 0;
-      } else {
-        const T* krow = k_cache + (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
-        float dot = 0.0f;
-        for (int d = 0; d < D; ++d) dot = fmaf(to_float(krow[d]), q_smem[warp][d], dot);
-        score = dot * scale_log2;
-      }
+  // one key at a time, the lanes spread over the head: every load is a coalesced row of the cache
+  for (int key = 0; key < kept; ++key) {
+    const int page = pages[key / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (lane == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      continue;
     }
-    const float new_max = fmaxf(running_max, warp_max(score));
-    const float p = (score == -INFINITY) ? 0.0f : exp2f(score - new_max);
+    const size_t at = (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
+    float dot = 0.0f;
+    for (int d = lane; d < D; d += 32) dot = fmaf(to_float(k_cache[at + d]), q_smem[warp][d], dot);
+    const float score = warp_sum(dot) * scale_log2;
+    const float new_max = fmaxf(running_max, score);
+    const float p = exp2f(score - new_max);
     const float correction = (running_max == -INFINITY) ? 0.0f : exp2f(running_max - new_max);
-    running_sum = running_sum * correction + warp_sum(p);
+    running_sum = running_sum * correction + p;
     running_max = new_max;
 #pragma unroll
-    for (int i = 0; i < SLICES; ++i) acc[i] *= correction;
-    const int count = min(32, kept - base);
-    for (int kk = 0; kk < count; ++kk) {
-      const float pk = __shfl_sync(0xffffffffu, p, kk);
-      const int pg = __shfl_sync(0xffffffffu, page, kk);
-      if (pg == 0) continue;
-      const T* vrow = v_cache + (size_t)pg * page_elems + head_off + (size_t)((base + kk) % page_size) * D;
-#pragma unroll
-      for (int i = 0; i < SLICES; ++i) {
-        const int d = lane + 32 * i;
-        if (d < D) acc[i] = fmaf(pk, to_float(vrow[d]), acc[i]);
-      }
+    for (int i = 0; i < SLICES; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] = fmaf(p, to_float(v_cache[at + d]), acc[i] * correction);
     }
   }
   if (!(running_sum > 0.0f)) return;

@@ -151,6 +151,7 @@ struct KvbTrace {
 #define KVB_TAG_MOE_GEMM 23
 #define KVB_TAG_MOE_COMBINE 24
 #define KVB_TAG_KEPT_FIRST 25
+#define KVB_TAG_MOE_GATHER 26
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

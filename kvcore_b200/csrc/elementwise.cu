@@ -493,16 +493,41 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
 // in 32-bit, rounded once.
 // ------------------------------------------------------------------------------------------
 template <typename T>
+__device__ __forceinline__ float glu_sigmoid_times(float g, float alpha);
+template <>
+__device__ __forceinline__ float glu_sigmoid_times<float>(float g, float alpha) { return g / (1.0f + expf(-alpha * g)); }
+// rounded to bf16 by the caller: the fast exponential and division are three orders inside that rounding
+template <>
+__device__ __forceinline__ float glu_sigmoid_times<bf16>(float g, float alpha) { return __fdividef(g, 1.0f + __expf(-alpha * g)); }
+
+template <typename T, bool VEC>
 __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, float alpha,
-                                   float limit, float shift, long long total) {
+                                   float limit, float shift, long long total_vecs) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_GLU_CLAMPED);
+  constexpr int N = VEC ? Vec16<T>::N : 1;
+  const int per_row = inter / N;
   const long long step = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += step) {
-    const long long row = i / inter;
-    const int col = (int)(i % inter);
-    const float g = fminf(to_float(gu[row * 2 * inter + col]), limit);
-    const float u = fminf(fmaxf(to_float(gu[row * 2 * inter + inter + col]), -limit), limit);
-    out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vecs; v += step) {
+    const long long row = v / per_row;
+    const int col = (int)(v % per_row) * N;
+    const T* g = gu + row * 2 * inter + col;
+    T* o = out + row * inter + col;
+    if (VEC) {
+      Vec16<T> a, b, r;
+      a.load(g);
+      b.load(g + inter);
+#pragma unroll
+      for (int j = 0; j < Vec16<T>::N; ++j) {
+        const float gate = fminf(a.get(j), limit);
+        const float up = fminf(fmaxf(b.get(j), -limit), limit);
+        r.set(j, glu_sigmoid_times<T>(gate, alpha) * (up + shift));
+      }
+      r.store(o);
+    } else {
+      const float gate = fminf(to_float(g[0]), limit);
+      const float up = fminf(fmaxf(to_float(g[inter]), -limit), limit);
+      o[0] = from_float<T>(glu_sigmoid_times<T>(gate, alpha) * (up + shift));
+    }
   }
 }
 
@@ -510,17 +535,20 @@ extern "C" int kvb_glu_clamped(void* out, const void* gate_up, int rows, int int
                                float shift, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   KVB_REQUIRE(inter > 0, "glu_clamped: width must be positive");
-  const long long total = (long long)rows * inter;
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const bool vec = ((size_t)inter * esize) % 16 == 0 && aligned16(out) && aligned16(gate_up);
+  const int n = vec ? 16 / esize : 1;
+  const long long total = (long long)rows * (inter / n);
   const int threads = 256;
   const long long wanted = (total + threads - 1) / threads;
   const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
   const int blocks = (int)(wanted < resident ? wanted : resident);
-  if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((glu_clamped_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true,
-                              (float*)out, (const float*)gate_up, inter, alpha, limit, shift, total));
-  else
-    KVB_CHECK_CUDA(kvb_launch((glu_clamped_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true,
-                              (bf16*)out, (const bf16*)gate_up, inter, alpha, limit, shift, total));
+#define KVB_GLU(T_, V_)                                                                                    \
+  KVB_CHECK_CUDA(kvb_launch((glu_clamped_kernel<T_, V_>), dim3(blocks), dim3(threads), 0, stream, true,    \
+                            (T_*)out, (const T_*)gate_up, inter, alpha, limit, shift, total))
+  if (dtype == KVB_F32) { if (vec) KVB_GLU(float, true); else KVB_GLU(float, false); }
+  else { if (vec) KVB_GLU(bf16, true); else KVB_GLU(bf16, false); }
+#undef KVB_GLU
   KVB_CHECK_LAUNCH();
   return 0;
 }

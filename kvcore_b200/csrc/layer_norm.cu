@@ -13,6 +13,70 @@
 #define LN_THREADS 256
 #define LN_KEEP 16   // values a thread keeps in registers between the passes (rows up to 4,096 wide)
 
+// Rows whose width is a multiple of 4 and at most 4,096, on 16-byte boundaries: a thread holds 4 neighbouring
+// columns per pass (one 16-byte load of a 32-bit row), the same three passes over registers.
+template <typename IN, typename OUT, typename W>
+__global__ void __launch_bounds__(LN_THREADS)
+layer_norm_vec4_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* __restrict__ weight,
+                       const W* __restrict__ bias, int width, float eps) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_LAYERNORM);
+  __shared__ float scratch[32];
+  const IN* row = x + (size_t)blockIdx.x * width;
+  OUT* orow = out + (size_t)blockIdx.x * width;
+  constexpr int PASSES = LN_KEEP / 4;
+  float mine[PASSES][4];
+  float sum = 0.0f;
+#pragma unroll
+  for (int s = 0; s < PASSES; ++s) {
+    const int i = (threadIdx.x + s * LN_THREADS) * 4;
+    if (i < width) {
+      if (sizeof(IN) == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        mine[s][0] = v.x; mine[s][1] = v.y; mine[s][2] = v.z; mine[s][3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mine[s][j] = to_float(row[i + j]);
+      }
+    } else {
+      mine[s][0] = mine[s][1] = mine[s][2] = mine[s][3] = 0.0f;
+    }
+    sum += (mine[s][0] + mine[s][1]) + (mine[s][2] + mine[s][3]);
+  }
+  const float mean = block_sum(sum, scratch) / (float)width;
+  float sq = 0.0f;
+#pragma unroll
+  for (int s = 0; s < PASSES; ++s) {
+    const int i = (threadIdx.x + s * LN_THREADS) * 4;
+    if (i < width) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float d = mine[s][j] - mean; sq = fmaf(d, d, sq); }
+    }
+  }
+  const float var = block_sum(sq, scratch) / (float)width;
+  const float inv = 1.0f / sqrtf(var + eps);
+#pragma unroll
+  for (int s = 0; s < PASSES; ++s) {
+    const int i = (threadIdx.x + s * LN_THREADS) * 4;
+    if (i < width) {
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        y[j] = (mine[s][j] - mean) * inv * to_float(weight[i + j]);
+        if (bias != nullptr) y[j] += to_float(bias[i + j]);
+      }
+      if (sizeof(OUT) == 4) {
+        *reinterpret_cast<float4*>(orow + i) = make_float4(y[0], y[1], y[2], y[3]);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<unsigned*>(&lo);
+        packed.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(orow + i) = packed;
+      }
+    }
+  }
+}
+
 template <typename IN, typename OUT, typename W>
 __global__ void __launch_bounds__(LN_THREADS)
 layer_norm_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* __restrict__ weight,
@@ -73,6 +137,9 @@ layer_norm_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* __re
 template <typename IN, typename OUT, typename W>
 static cudaError_t launch_layer_norm(void* out, const void* x, const void* w, const void* b, int rows, int width,
                                      float eps, cudaStream_t stream) {
+  if (width % 4 == 0 && width <= LN_THREADS * LN_KEEP && aligned16(out) && aligned16(x))
+    return kvb_launch((layer_norm_vec4_kernel<IN, OUT, W>), dim3(rows), dim3(LN_THREADS), 0, stream, true,
+                      (OUT*)out, (const IN*)x, (const W*)w, (const W*)b, width, eps);
   return kvb_launch((layer_norm_kernel<IN, OUT, W>), dim3(rows), dim3(LN_THREADS), 0, stream, true,
                     (OUT*)out, (const IN*)x, (const W*)w, (const W*)b, width, eps);
 }

@@ -6,14 +6,19 @@
 //            the chosen scores, optionally divided by their sum.  Extra rows (a shared expert's gate) are
 //            dotted the same way and leave sigmoid(row . x).
 //   align:   pairs p = token * top + slot are laid out expert by expert, each expert's run padded to whole
-//            tiles of MOE_BM rows with -1, with the expert of every tile and the number of tiles used.
+//            tiles of MOE_BM rows with -1, with the expert of every tile and the number of tiles used
+//            (optionally also the row of every pair and where each expert's run begins).
 //            Launch sizes depend on the batch's shape only: blocks beyond the tiles used leave at once.
 //   gemm:    out[p, n] = sum_k a(p, k) * w[expert(p), n, k], one accumulator per output taking its
 //            products in ascending k, so a pair's result depends on nothing else in the batch.
 //            a(p, k) = A[p / a_row_div, k] (* pair weight, rounded to the storage type): the weight
 //            multiplies the expert's INPUT.  GATED: w holds gate rows [0, N) and up rows [N, 2N) and
 //            out = silu(gate) * up.
-//   combine: y[token] = sum over slots of out[token * top + slot] (ascending slot, 32-bit)
+//   gemv:    the same two products for a handful of pairs in bf16, bound by the bytes of the chosen
+//            experts' matrices (no padded tiles).
+//   gather:  the pairs' input rows expert by expert at a common stride, for one batched library product
+//            over all experts.
+//   combine: y[token] = sum over slots of out[row of (token, slot)] (ascending slot, 32-bit)
 //            (+ gate[token] * shared[token]).
 #include "common.cuh"
 
@@ -112,6 +117,7 @@ extern "C" int kvb_moe_route(int* ids_out, float* weights_out, float* gate_out, 
 // tile_expert [capacity / MOE_BM], meta[0] = tiles used.
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ meta,
+                 int* __restrict__ row_of_pair, int* __restrict__ expert_begin,
                  const int* __restrict__ ids, int pairs, int E, int capacity, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_ALIGN);
   extern __shared__ int ismem[];
@@ -136,16 +142,26 @@ moe_align_kernel(int* __restrict__ sorted, int* __restrict__ tile_expert, int* _
       counts[e] = 0;   // becomes the fill cursor
     }
     meta[0] = at / MOE_BM;
+    if (expert_begin != nullptr) {   // where each expert's (padded) run of rows begins, and the end of the last
+      for (int e = 0; e < E; ++e) expert_begin[e] = offsets[e];
+      expert_begin[E] = at;
+    }
   }
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     const int e = ids[p];
-    if (e >= 0 && e < E) sorted[offsets[e] + atomicAdd(&counts[e], 1)] = p;
+    if (e >= 0 && e < E) {
+      const int row = offsets[e] + atomicAdd(&counts[e], 1);
+      sorted[row] = p;
+      if (row_of_pair != nullptr) row_of_pair[p] = row;
+    } else if (row_of_pair != nullptr) {
+      row_of_pair[p] = -1;
+    }
   }
 }
 
-extern "C" int kvb_moe_align(int* sorted, int* tile_expert, int* meta, const int* ids, int pairs, int E,
-                             int capacity, cudaStream_t stream) {
+extern "C" int kvb_moe_align(int* sorted, int* tile_expert, int* meta, int* row_of_pair, int* expert_begin,
+                             const int* ids, int pairs, int E, int capacity, cudaStream_t stream) {
   if (pairs == 0) return 0;
   KVB_REQUIRE(E > 0 && E <= 8192, "moe_align: between 1 and 8192 experts");
   // tiles used: one per started run of MOE_BM pairs of an expert, so at most one per pair
@@ -155,7 +171,7 @@ extern "C" int kvb_moe_align(int* sorted, int* tile_expert, int* meta, const int
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "moe_align: no status word");
   KVB_CHECK_CUDA(kvb_launch((moe_align_kernel), dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, true,
-                            sorted, tile_expert, meta, ids, pairs, E, capacity, status));
+                            sorted, tile_expert, meta, row_of_pair, expert_begin, ids, pairs, E, capacity, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
@@ -256,40 +272,231 @@ extern "C" int kvb_moe_gemm(void* out, const void* a, long long a_stride, int a_
   return 0;
 }
 
-template <typename T>
-__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ expert_out, int top,
-                                   const T* __restrict__ shared, const float* __restrict__ gate, int gate_stride,
-                                   int width, long long total) {
-  KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_COMBINE);
-  const long long step = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += step) {
-    const long long token = i / width;
-    const int col = (int)(i % width);
-    float acc = 0.0f;
-    for (int slot = 0; slot < top; ++slot) acc += to_float(expert_out[((size_t)token * top + slot) * width + col]);
-    if (shared != nullptr) {
-      const float s = to_float(shared[i]);
-      acc += gate != nullptr ? gate[(size_t)token * gate_stride] * s : s;
+// Decode-sized batches in bf16: one pass over each chosen expert's matrices.  grid (N / 32, pairs): a block
+// holds the pair's input row (weighted and rounded) in shared memory; each of its 8 warps owns 4 output
+// columns (GATED: the 4 gate rows and the 4 up rows) and walks K in 16-byte loads, lane-strided, the four
+// rows' loads in flight together; a butterfly sums the lanes.  No tile is padded with rows that are not
+// there, so the kernel is bound by the weights it reads.
+#define MOE_GEMV_COLS 32
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, long long a_stride, int a_row_div,
+                const float* __restrict__ pair_weight, const bf16* __restrict__ w, const int* __restrict__ ids,
+                int E, int N, int K, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_GEMM);
+  extern __shared__ __align__(16) unsigned char gemv_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(gemv_smem);
+  const int pair = blockIdx.y;
+  const int expert = ids[pair];
+  if (expert < 0 || expert >= E) {
+    if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_TOKEN);
+    return;
+  }
+  const bf16* row = a + (size_t)(pair / a_row_div) * a_stride;
+  const float scale = pair_weight != nullptr ? pair_weight[pair] : 1.0f;
+  for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+    Vec16<bf16> v;
+    v.load(row + k);
+    if (pair_weight != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v.set(j, v.get(j) * scale);
     }
-    out[i] = from_float<T>(acc);
+    v.store(xs + k);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * MOE_GEMV_COLS + warp * 4;
+  const bf16* we = w + (size_t)expert * (GATED ? 2 : 1) * N * K;
+  constexpr int ROWS = GATED ? 8 : 4;
+  const bf16* rows[ROWS];
+  float acc[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int n = min(n0 + (r & 3), N - 1) + (r >= 4 ? N : 0);
+    rows[r] = we + (size_t)n * K;
+    acc[r] = 0.0f;
+  }
+  for (int k = lane * 8; k < K; k += 32 * 8) {
+    Vec16<bf16> x, wv[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) wv[r].load(rows[r] + k);
+    x.load(xs + k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float xv = x.get(j);
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(wv[r].get(j), xv, acc[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+  if (lane < 4 && n0 + lane < N) {
+    float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+    if (GATED) {
+      const float u = lane == 0 ? acc[4 % ROWS] : lane == 1 ? acc[5 % ROWS] : lane == 2 ? acc[6 % ROWS] : acc[7 % ROWS];
+      const float g = to_float(from_float<bf16>(v));
+      v = to_float(from_float<bf16>(moe_silu<bf16>(g))) * to_float(from_float<bf16>(u));
+    }
+    out[(size_t)pair * N + n0 + lane] = from_float<bf16>(v);
   }
 }
 
-extern "C" int kvb_moe_combine(void* out, const void* expert_out, int tokens, int top, const void* shared,
-                               const float* gate, int gate_stride, int width, int dtype, cudaStream_t stream) {
+extern "C" int kvb_moe_gemv(void* out, const void* a, long long a_stride, int a_row_div, const float* pair_weight,
+                            const void* w, const int* ids, int pairs, int E, int N, int K, int gated,
+                            cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  KVB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && a_stride % 8 == 0 && a_row_div > 0, "moe_gemv: K and the row stride must be multiples of 8");
+  KVB_REQUIRE(aligned16(a) && aligned16(w), "moe_gemv: operands must be 16-byte aligned");
+  KVB_REQUIRE(pairs <= 65535, "moe_gemv: too many pairs for one launch");
+  const size_t smem = (size_t)K * sizeof(bf16);
+  KVB_REQUIRE(smem <= 200 * 1024, "moe_gemv: an input row does not fit in shared memory");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "moe_gemv: no status word");
+  dim3 grid((N + MOE_GEMV_COLS - 1) / MOE_GEMV_COLS, pairs);
+#define KVB_MOE_GEMV(G_)                                                                                       \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(moe_gemv_kernel<G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    KVB_CHECK_CUDA(kvb_launch((moe_gemv_kernel<G_>), grid, dim3(256), smem, stream, true, (bf16*)out, (const bf16*)a, \
+                              a_stride, a_row_div, pair_weight, (const bf16*)w, ids, E, N, K, status));        \
+  } while (0)
+  if (gated) KVB_MOE_GEMV(true); else KVB_MOE_GEMV(false);
+#undef KVB_MOE_GEMV
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// Rows in the grouped order for batched library products: expert e owns rows [e * C, (e + 1) * C) of `out`;
+// row e * C + j holds weight(p) * a[p / a_row_div] for the j-th pair p of the expert (sorted[expert_begin[e] + j]),
+// zeros beyond the expert's pairs.  row_of_pair[p] is set to the row that pair p got.
+template <typename T, bool VEC>
+__global__ void moe_gather_kernel(T* __restrict__ out, const T* __restrict__ a, long long a_stride, int a_row_div,
+                                  const float* __restrict__ pair_weight, const int* __restrict__ sorted,
+                                  const int* __restrict__ expert_begin, int C, int* __restrict__ row_of_pair, int K) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_GATHER);
+  const int e = blockIdx.x / C, j = blockIdx.x % C;
+  const int at = expert_begin[e] + j;
+  const int pair = at < expert_begin[e + 1] ? sorted[at] : -1;
+  T* dst = out + (size_t)blockIdx.x * K;
+  constexpr int N = VEC ? Vec16<T>::N : 1;
+  if (pair < 0) {
+    for (int k = threadIdx.x * N; k < K; k += blockDim.x * N) {
+      if (VEC) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+      else dst[k] = from_float<T>(0.0f);
+    }
+    return;
+  }
+  if (threadIdx.x == 0) row_of_pair[pair] = blockIdx.x;
+  const T* src = a + (size_t)(pair / a_row_div) * a_stride;
+  const float scale = pair_weight != nullptr ? pair_weight[pair] : 1.0f;
+  for (int k = threadIdx.x * N; k < K; k += blockDim.x * N) {
+    if (VEC) {
+      Vec16<T> v;
+      v.load(src + k);
+      if (pair_weight != nullptr) {
+#pragma unroll
+        for (int i = 0; i < Vec16<T>::N; ++i) v.set(i, v.get(i) * scale);
+      }
+      v.store(dst + k);
+    } else {
+      dst[k] = pair_weight != nullptr ? from_float<T>(to_float(src[k]) * scale) : src[k];
+    }
+  }
+}
+
+extern "C" int kvb_moe_gather(void* out, const void* a, long long a_stride, int a_row_div, const float* pair_weight,
+                              const int* sorted, const int* expert_begin, int E, int C, int* row_of_pair, int K,
+                              int dtype, cudaStream_t stream) {
+  if (E == 0 || C == 0) return 0;
+  KVB_REQUIRE(K > 0 && a_row_div > 0 && row_of_pair != nullptr, "moe_gather: empty rows");
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const bool vec = ((size_t)K * esize) % 16 == 0 && ((size_t)a_stride * esize) % 16 == 0 && aligned16(out) && aligned16(a);
+  const long long rows = (long long)E * C;
+  KVB_REQUIRE(rows < (1ll << 31), "moe_gather: too many rows");
+#define KVB_GATHER(T_, V_)                                                                                  \
+  KVB_CHECK_CUDA(kvb_launch((moe_gather_kernel<T_, V_>), dim3((int)rows), dim3(128), 0, stream, true, (T_*)out, \
+                            (const T_*)a, a_stride, a_row_div, pair_weight, sorted, expert_begin, C, row_of_pair, K))
+  if (dtype == KVB_F32) { if (vec) KVB_GATHER(float, true); else KVB_GATHER(float, false); }
+  else { if (vec) KVB_GATHER(bf16, true); else KVB_GATHER(bf16, false); }
+#undef KVB_GATHER
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+template <typename T, bool VEC>
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ expert_out, int top,
+                                   const int* __restrict__ row_of_pair, const float* __restrict__ pair_weight,
+                                   const T* __restrict__ shared, const float* __restrict__ gate, int gate_stride,
+                                   int width, long long total_vecs) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_COMBINE);
+  constexpr int N = VEC ? Vec16<T>::N : 1;
+  const int per_row = width / N;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vecs; v += step) {
+    const long long token = v / per_row;
+    const int col = (int)(v % per_row) * N;
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.0f;
+    for (int slot = 0; slot < top; ++slot) {
+      const long long pair = token * top + slot;
+      const long long row = row_of_pair != nullptr ? row_of_pair[pair] : pair;
+      if (row < 0) continue;
+      const float w = pair_weight != nullptr ? pair_weight[pair] : 1.0f;
+      const T* src = expert_out + (size_t)row * width + col;
+      if (VEC) {
+        Vec16<T> x;
+        x.load(src);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += pair_weight != nullptr ? w * x.get(j) : x.get(j);
+      } else {
+        acc[0] += pair_weight != nullptr ? w * to_float(src[0]) : to_float(src[0]);
+      }
+    }
+    if (shared != nullptr) {
+      const float g = gate != nullptr ? gate[(size_t)token * gate_stride] : 1.0f;
+      const T* src = shared + (size_t)token * width + col;
+      if (VEC) {
+        Vec16<T> x;
+        x.load(src);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += gate != nullptr ? g * x.get(j) : x.get(j);
+      } else {
+        acc[0] += gate != nullptr ? g * to_float(src[0]) : to_float(src[0]);
+      }
+    }
+    T* dst = out + (size_t)token * width + col;
+    if (VEC) {
+      Vec16<T> y;
+#pragma unroll
+      for (int j = 0; j < N; ++j) y.set(j, acc[j]);
+      y.store(dst);
+    } else {
+      dst[0] = from_float<T>(acc[0]);
+    }
+  }
+}
+
+extern "C" int kvb_moe_combine(void* out, const void* expert_out, int tokens, int top, const int* row_of_pair,
+                               const float* pair_weight, const void* shared, const float* gate, int gate_stride,
+                               int width, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   KVB_REQUIRE(width > 0 && top >= 0, "moe_combine: empty rows");
-  const long long total = (long long)tokens * width;
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const bool vec = ((size_t)width * esize) % 16 == 0 && aligned16(out) && aligned16(expert_out) &&
+                   (shared == nullptr || aligned16(shared));
+  const long long total = (long long)tokens * (width / (vec ? 16 / esize : 1));
   const int threads = 256;
   const long long wanted = (total + threads - 1) / threads;
   const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
   const int blocks = (int)(wanted < resident ? wanted : resident);
-  if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((moe_combine_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out,
-                              (const float*)expert_out, top, (const float*)shared, gate, gate_stride, width, total));
-  else
-    KVB_CHECK_CUDA(kvb_launch((moe_combine_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true, (bf16*)out,
-                              (const bf16*)expert_out, top, (const bf16*)shared, gate, gate_stride, width, total));
+#define KVB_COMBINE(T_, V_)                                                                                   \
+  KVB_CHECK_CUDA(kvb_launch((moe_combine_kernel<T_, V_>), dim3(blocks), dim3(threads), 0, stream, true, (T_*)out, \
+                            (const T_*)expert_out, top, row_of_pair, pair_weight, (const T_*)shared, gate,     \
+                            gate_stride, width, total))
+  if (dtype == KVB_F32) { if (vec) KVB_COMBINE(float, true); else KVB_COMBINE(float, false); }
+  else { if (vec) KVB_COMBINE(bf16, true); else KVB_COMBINE(bf16, false); }
+#undef KVB_COMBINE
   KVB_CHECK_LAUNCH();
   return 0;
 }

@@ -25,7 +25,7 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
                   const W* __restrict__ q_weight, const W* __restrict__ k_weight,
                   const int* __restrict__ table, int table_stride, T* __restrict__ k_cache,
                   T* __restrict__ v_cache, int H, int KVH, int D, int rot, int norm_mode, int value_mode,
-                  float eps, int page_size, int num_pages, int* status) {
+                  float eps, int page_size, int num_pages, int vec, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_QK_PREPARE);
   extern __shared__ float smem[];
   const int heads = H + KVH;
@@ -37,7 +37,17 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   T* row = rows + (size_t)token * row_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = QKP_THREADS / 32;
 
-  for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[i] = to_float(row[i]);
+  constexpr int VN = Vec16<T>::N;   // `vec`: rows, heads and cache rows start on 16-byte boundaries
+  if (vec) {
+    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+      Vec16<T> v;
+      v.load(row + i);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) x[i + j] = v.get(j);
+    }
+  } else {
+    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[i] = to_float(row[i]);
+  }
   __syncthreads();
 
   size_t cache_base = 0;
@@ -53,9 +63,18 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   const size_t head_stride = (size_t)page_size * D;
   if (write) {
     const T* v = value_mode == 1 ? row + (size_t)H * D : row + (size_t)(H + KVH) * D;
-    for (int i = threadIdx.x; i < KVH * D; i += QKP_THREADS) {
-      const int vh = i / D, d = i % D;
-      v_cache[cache_base + (size_t)vh * head_stride + d] = v[i];
+    if (vec) {
+      for (int i = threadIdx.x * VN; i < KVH * D; i += QKP_THREADS * VN) {
+        const int vh = i / D, d = i % D;
+        Vec16<T> t;
+        t.load(v + i);
+        t.store(v_cache + cache_base + (size_t)vh * head_stride + d);
+      }
+    } else {
+      for (int i = threadIdx.x; i < KVH * D; i += QKP_THREADS) {
+        const int vh = i / D, d = i % D;
+        v_cache[cache_base + (size_t)vh * head_stride + d] = v[i];
+      }
     }
   }
 
@@ -104,6 +123,19 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   }
 
   __syncthreads();   // the values were copied from the row that is overwritten now
+  if (vec) {
+    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+      Vec16<T> v;
+#pragma unroll
+      for (int j = 0; j < VN; ++j) v.set(j, x[i + j]);
+      v.store(row + i);
+      if (i >= H * D && write) {
+        const int kh = (i - H * D) / D, d = (i - H * D) % D;
+        v.store(k_cache + cache_base + (size_t)kh * head_stride + d);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
     const T v = from_float<T>(x[i]);
     row[i] = v;
@@ -133,6 +165,9 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   KVB_REQUIRE(status != nullptr, "qk_prepare: no status word");
   const size_t smem = ((size_t)(H + KVH) * D + 2 * (size_t)(H + KVH)) * sizeof(float);
   KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&
+                  (k_cache == nullptr || (aligned16(k_cache) && aligned16(v_cache)));
 #define KVB_QKP(T_, W_)                                                                                     \
   do {                                                                                                      \
     if (smem > 48 * 1024)                                                                                   \
@@ -140,7 +175,7 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
     KVB_CHECK_CUDA(kvb_launch((qk_prepare_kernel<T_, W_>), dim3(tokens), dim3(QKP_THREADS), smem, stream, true, \
                               (T_*)rows, row_stride, positions, req_index, (const float2*)cos_sin,          \
                               (const W_*)q_weight, (const W_*)k_weight, table, table_stride, (T_*)k_cache,  \
-                              (T_*)v_cache, H, KVH, D, rot, norm_mode, value_mode, eps, page_size, num_pages, status)); \
+                              (T_*)v_cache, H, KVH, D, rot, norm_mode, value_mode, eps, page_size, num_pages, vec, status)); \
   } while (0)
   if (dtype == KVB_F32) {
     KVB_REQUIRE(weight_dtype == KVB_F32, "qk_prepare: a 32-bit model needs 32-bit norm weights");

@@ -52,9 +52,11 @@ def ensure_built(verbose: bool = False) -> str:
                            _int, _int, _float, _int, _int, _int, _int, _vp],
         "kvb_glu_clamped": [_vp, _vp, _int, _int, _float, _float, _float, _int, _vp],
         "kvb_moe_route": [_vp, _vp, _vp, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _vp],
-        "kvb_moe_align": [_vp, _vp, _vp, _vp, _int, _int, _int, _vp],
+        "kvb_moe_align": [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _vp],
+        "kvb_moe_gemv": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_moe_gather": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _int, _int, _vp, _int, _int, _vp],
         "kvb_moe_gemm": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
-        "kvb_moe_combine": [_vp, _vp, _int, _int, _vp, _vp, _int, _int, _int, _vp],
+        "kvb_moe_combine": [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _int, _int, _int, _vp],
         "kvb_flash_paged_attention": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int,
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp, _vp],
         "kvb_kept_first_merge": [_vp, _int, _vp, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
@@ -636,7 +638,7 @@ STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 _stream_scratch: dict[int, torch.Tensor] = {}
 
 
-TRACE_TAGS = {25: "kept_first_merge", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+TRACE_TAGS = {25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
@@ -1018,13 +1020,86 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, score: str = "
     return ids, weights, gates
 
 
+# bf16 batches of at most this many (token, expert) pairs take the kernel that streams each chosen expert's
+# matrices once; larger ones take library products over each expert's run of rows
+MOE_GEMV_MAX_PAIRS = int(os.environ.get("KVCORE_B200_MOE_GEMV_PAIRS", "256"))
+
+
+class ExpertRows:
+    """What ``moe_experts`` leaves for ``moe_combine``: the experts' outputs ``rows [R, N]``, where the row of
+    pair ``t * top + s`` is that index itself (``row_of_pair`` None) or ``row_of_pair[t * top + s]``, and
+    weights still to be applied (``pending_weights`` [T * top], or None)."""
+
+    __slots__ = ("rows", "row_of_pair", "pending_weights")
+
+    def __init__(self, rows, row_of_pair=None, pending_weights=None):
+        self.rows, self.row_of_pair, self.pending_weights = rows, row_of_pair, pending_weights
+
+
+class ExpertGrouping:
+    """The (token, expert) pairs of a batch laid out expert by expert (``moe_group``), with the experts' row
+    counts on their way to the host: ``begins()`` waits for that copy alone, not for the stream."""
+
+    __slots__ = ("sorted_pairs", "tile_expert", "meta", "row_of_pair", "expert_begin", "max_tiles", "capacity",
+                 "_host", "_ready")
+
+    def begins(self) -> list[int]:
+        self._ready.synchronize()
+        return self._host.tolist()
+
+
+def moe_group(ids: torch.Tensor, experts: int, *, for_library: bool) -> ExpertGrouping:
+    """Group the pairs ``t * top + s`` of ``ids [T, top]`` by expert.  ``for_library``: also the row of every
+    pair and where each expert's run begins, the latter copied to pinned host memory behind an event, so that
+    a caller who has other work to launch first (a layer whose mixer runs beside its feed-forward) finds the
+    counts there when it comes back, without draining the stream."""
+    _check(ids, "ids", dtype=torch.int32)
+    pairs = ids.numel()
+    tile = int(_lib.kvb_moe_tile_rows())
+    g = ExpertGrouping()
+    g.max_tiles = min(-(-(pairs + experts * (tile - 1)) // tile), pairs)
+    g.capacity = g.max_tiles * tile
+    g.sorted_pairs = torch.empty(g.capacity, dtype=torch.int32, device=ids.device)
+    g.tile_expert = torch.empty(g.max_tiles, dtype=torch.int32, device=ids.device)
+    g.meta = torch.empty(4, dtype=torch.int32, device=ids.device)
+    g.row_of_pair = torch.empty(pairs, dtype=torch.int32, device=ids.device) if for_library else None
+    g.expert_begin = torch.empty(experts + 1, dtype=torch.int32, device=ids.device) if for_library else None
+    g._host = g._ready = None
+    _call("kvb_moe_align", g.sorted_pairs.data_ptr(), g.tile_expert.data_ptr(), g.meta.data_ptr(),
+          None if g.row_of_pair is None else g.row_of_pair.data_ptr(),
+          None if g.expert_begin is None else g.expert_begin.data_ptr(), ids.data_ptr(), pairs, experts, g.capacity,
+          _stream())
+    if for_library:
+        g._host = torch.empty(experts + 1, dtype=torch.int32, pin_memory=True)
+        g._host.copy_(g.expert_begin, non_blocking=True)
+        g._ready = torch.cuda.Event()
+        g._ready.record()
+    return g
+
+
+def moe_path(x: torch.Tensor, pairs: int, ff: int) -> str:
+    """Which way ``moe_experts`` takes for a batch of ``pairs`` (token, expert) pairs of ``x``'s type."""
+    if x.dtype != torch.bfloat16:
+        return "tiles"
+    if pairs <= MOE_GEMV_MAX_PAIRS and x.shape[1] % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0:
+        return "stream"
+    return "library" if not torch.cuda.is_current_stream_capturing() else "tiles"
+
+
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
-                down: torch.Tensor, *, weight_on_input: bool) -> torch.Tensor:
-    """The chosen experts of every token: ``out [T * top, N]``, row ``t * top + s`` holding
-    ``down[e] @ (silu(gate[e] @ a) * (up[e] @ a))`` for ``e = ids[t, s]``.  ``weight_on_input``:
-    ``a = weights[t, s] * x[t]`` (rounded to the storage type).  Otherwise ``a = x[t]`` and the weight
-    multiplies the rows that enter the last product, which weights the output, that product being linear.
-    ``gate_up [E, 2F, K]`` (gate rows first), ``down [E, N, F]``."""
+                down: torch.Tensor, *, weight_on_input: bool, path: str | None = None,
+                grouping: ExpertGrouping | None = None) -> ExpertRows:
+    """The chosen experts of every token: for pair ``t * top + s`` with ``e = ids[t, s]``,
+    ``down[e] @ (silu(gate[e] @ a) * (up[e] @ a))``.  ``weight_on_input``: ``a = weights[t, s] * x[t]``
+    (rounded to the storage type).  Otherwise ``a = x[t]`` and the weight multiplies the output (the rows
+    that enter the last product, or the sum in ``moe_combine``: that product is linear).
+    ``gate_up [E, 2F, K]`` (gate rows first), ``down [E, N, F]``.
+
+    Three ways, by ``path`` (default: by type and size).  "tiles": grouped products of this library, one
+    accumulator per output in ascending k (all of float32: bit-equal under any batching).  "stream": bf16,
+    a handful of pairs, one pass over each chosen expert's matrices.  "library": bf16 prompts, the pairs'
+    rows gathered expert by expert at a common stride and one batched library product per matrix over all
+    experts (the experts' row counts are read back from the device once per call)."""
     _check(x, "x", contiguous=False)
     _check(ids, "ids", dtype=torch.int32)
     _check(weights, "weights", dtype=torch.float32)
@@ -1038,15 +1113,51 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_
     if gate_up.shape[2] != k or down.shape != (experts, n, ff) or x.stride(1) != 1:
         raise KernelError("moe_experts: the experts' matrices do not match the input")
     pairs = tokens * top
-    tile = int(_lib.kvb_moe_tile_rows()) if _lib is not None else 16
-    max_tiles = min(-(-(pairs + experts * (tile - 1)) // tile), pairs)
-    capacity = max_tiles * tile
-    sorted_pairs = torch.empty(capacity, dtype=torch.int32, device=x.device)
-    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=x.device)
-    meta = torch.empty(4, dtype=torch.int32, device=x.device)
-    _call("kvb_moe_align", sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), ids.data_ptr(), pairs,
-          experts, capacity, _stream())
     code = _dtype_code(x)
+    if path is None:
+        path = moe_path(x, pairs, ff)
+    if path == "stream":
+        hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+        _call("kvb_moe_gemv", hidden.data_ptr(), x.data_ptr(), x.stride(0), top,
+              weights.data_ptr() if weight_on_input else None, gate_up.data_ptr(), ids.data_ptr(), pairs, experts,
+              ff, k, 1, _stream())
+        out = torch.empty((pairs, n), dtype=x.dtype, device=x.device)
+        _call("kvb_moe_gemv", out.data_ptr(), hidden.data_ptr(), hidden.stride(0), 1,
+              None if weight_on_input else weights.data_ptr(), down.data_ptr(), ids.data_ptr(), pairs, experts,
+              n, ff, 0, _stream())
+        return ExpertRows(out)
+    library = path == "library"
+    if grouping is None or (library and grouping.expert_begin is None):
+        grouping = moe_group(ids, experts, for_library=library)
+    tile = int(_lib.kvb_moe_tile_rows())
+    sorted_pairs, tile_expert, meta = grouping.sorted_pairs, grouping.tile_expert, grouping.meta
+    row_of_pair, expert_begin = grouping.row_of_pair, grouping.expert_begin
+    max_tiles, capacity = grouping.max_tiles, grouping.capacity
+    if library:
+        begins = grouping.begins()                # the one read-back: how many rows each expert got
+        stride = max(begins[e + 1] - begins[e] for e in range(experts))    # a multiple of the tile's rows
+        gathered = torch.empty((experts, stride, k), dtype=x.dtype, device=x.device)
+        _call("kvb_moe_gather", gathered.data_ptr(), x.data_ptr(), x.stride(0), top,
+              weights.data_ptr() if weight_on_input else None, sorted_pairs.data_ptr(), expert_begin.data_ptr(),
+              experts, stride, row_of_pair.data_ptr(), k, code, _stream())
+        # every expert's rows at one stride: two batched library products over all experts (an expert with
+        # fewer pairs multiplies zero rows; with one expert far fuller than the rest, expert by expert instead)
+        if experts * stride <= 2 * capacity + experts * tile:
+            both = torch.bmm(gathered, gate_up.transpose(1, 2))
+            hidden = silu_mul(both.view(experts * stride, two_ff), 0).view(experts, stride, ff)
+            out = torch.bmm(hidden, down.transpose(1, 2)).view(experts * stride, n)
+        else:
+            both = torch.zeros((experts, stride, two_ff), dtype=x.dtype, device=x.device)
+            for e in range(experts):
+                if begins[e + 1] > begins[e]:
+                    torch.mm(gathered[e, : begins[e + 1] - begins[e]], gate_up[e].t(), out=both[e, : begins[e + 1] - begins[e]])
+            hidden = silu_mul(both.view(experts * stride, two_ff), 0).view(experts, stride, ff)
+            out = torch.empty((experts, stride, n), dtype=x.dtype, device=x.device)
+            for e in range(experts):
+                if begins[e + 1] > begins[e]:
+                    torch.mm(hidden[e, : begins[e + 1] - begins[e]], down[e].t(), out=out[e, : begins[e + 1] - begins[e]])
+            out = out.view(experts * stride, n)
+        return ExpertRows(out, row_of_pair, None if weight_on_input else weights.reshape(-1))
     hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
     _call("kvb_moe_gemm", hidden.data_ptr(), x.data_ptr(), x.stride(0), top,
           weights.data_ptr() if weight_on_input else None, gate_up.data_ptr(), sorted_pairs.data_ptr(),
@@ -1055,28 +1166,34 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_
     _call("kvb_moe_gemm", out.data_ptr(), hidden.data_ptr(), hidden.stride(0), 1,
           None if weight_on_input else weights.data_ptr(), down.data_ptr(), sorted_pairs.data_ptr(),
           tile_expert.data_ptr(), meta.data_ptr(), max_tiles, n, ff, 0, code, _stream())
-    return out
+    return ExpertRows(out)
 
 
-def moe_combine(expert_out: torch.Tensor, tokens: int, top: int, shared: torch.Tensor | None = None,
+def moe_combine(expert_out, tokens: int, top: int, shared: torch.Tensor | None = None,
                 gates: torch.Tensor | None = None) -> torch.Tensor:
-    """``y[t] = sum_s expert_out[t * top + s] (+ gates[t, 0] * shared[t])``, summed in 32-bit in slot order."""
-    _check(expert_out, "expert_out")
-    width = expert_out.shape[1]
-    if expert_out.shape[0] != tokens * top:
+    """``y[t] = sum_s rows[row of pair t * top + s] (+ gates[t, 0] * shared[t])``, summed in 32-bit in slot
+    order; ``expert_out`` is what ``moe_experts`` returned (or a plain ``[T * top, N]`` tensor)."""
+    if not isinstance(expert_out, ExpertRows):
+        expert_out = ExpertRows(expert_out)
+    rows = expert_out.rows
+    _check(rows, "expert_out")
+    width = rows.shape[1]
+    if expert_out.row_of_pair is None and rows.shape[0] != tokens * top:
         raise KernelError("moe_combine: one row per (token, slot) is needed")
     if shared is not None:
-        _check(shared, "shared", dtype=expert_out.dtype)
+        _check(shared, "shared", dtype=rows.dtype)
         if tuple(shared.shape) != (tokens, width):
             raise KernelError("moe_combine: the shared expert's rows do not match")
     if gates is not None:
         _check(gates, "gates", dtype=torch.float32)
         if shared is None or gates.shape[0] != tokens:
             raise KernelError("moe_combine: gates need the shared rows they multiply")
-    out = torch.empty((tokens, width), dtype=expert_out.dtype, device=expert_out.device)
-    _call("kvb_moe_combine", out.data_ptr(), expert_out.data_ptr(), tokens, top,
+    out = torch.empty((tokens, width), dtype=rows.dtype, device=rows.device)
+    _call("kvb_moe_combine", out.data_ptr(), rows.data_ptr(), tokens, top,
+          None if expert_out.row_of_pair is None else expert_out.row_of_pair.data_ptr(),
+          None if expert_out.pending_weights is None else expert_out.pending_weights.data_ptr(),
           None if shared is None else shared.data_ptr(), None if gates is None else gates.data_ptr(),
-          0 if gates is None else gates.stride(0), width, _dtype_code(expert_out), _stream())
+          0 if gates is None else gates.stride(0), width, _dtype_code(rows), _stream())
     return out
 
 
@@ -1109,6 +1226,8 @@ __all__ = [
     "library_is_loaded",
     "moe_combine",
     "moe_experts",
+    "moe_group",
+    "moe_path",
     "moe_route",
     "qk_prepare",
     "stream_add",

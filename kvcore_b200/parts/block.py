@@ -104,10 +104,19 @@ class ParallelResidualBlock(Block):
             stream = residual if residual.dtype == torch.float32 else K.stream_add(residual)
             if not isinstance(h, Summed):          # a block in front left its last output unsummed
                 stream = K.stream_add(stream, h)
+        # Both sub-layers read the same stream, so a feed-forward that has something to get ready (a
+        # ``prepare(x, ctx)`` whose result ``forward`` takes: a router whose grouping the host must see)
+        # does that ahead of the mixer's launches, and nothing waits for it later.
+        fx = prepared = None
+        if self.feed_forward is not None:
+            fx = self.feed_forward_norm.forward(stream)
+            prepare = getattr(self.feed_forward, "prepare", None)
+            prepared = None if prepare is None else prepare(fx, ctx)
         a = self.mixer.forward(self.mixer_norm.forward(stream), ctx, cache)
         f = None
         if self.feed_forward is not None:
-            f = self.feed_forward.forward(self.feed_forward_norm.forward(stream), ctx)
+            f = (self.feed_forward.forward(fx, ctx) if prepared is None
+                 else self.feed_forward.forward(fx, ctx, prepared))
         return Summed(None), K.stream_add(stream, a, f)
 
 

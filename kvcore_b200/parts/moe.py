@@ -87,11 +87,21 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             self.shared.finalize_weights()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        ids, weights, gates = K.moe_route(x, self.router_weight, self.top_k, score=self.score,
-                                          renormalize=self.renormalize, gate_rows=self.shared_gate_weight)
+    def prepare(self, x: torch.Tensor, ctx):
+        """The router and the grouping of the pairs by expert, ahead of ``forward``: a block that has other
+        work to launch in between (its mixer) calls this first, so that what the host must know of the
+        grouping has arrived by the time ``forward`` asks for it."""
+        routed = K.moe_route(x, self.router_weight, self.top_k, score=self.score,
+                             renormalize=self.renormalize, gate_rows=self.shared_gate_weight)
+        grouping = None
+        if K.moe_path(x, x.shape[0] * self.top_k, self.expert_size) == "library":
+            grouping = K.moe_group(routed[0], self.num_experts, for_library=True)
+        return routed, grouping
+
+    def forward(self, x: torch.Tensor, ctx, prepared=None) -> torch.Tensor:
+        (ids, weights, gates), grouping = prepared if prepared is not None else self.prepare(x, ctx)
         pairs = K.moe_experts(x, ids, weights, self.gate_up_weight, self.down_weight,
-                              weight_on_input=self.weight_on == "input")
+                              weight_on_input=self.weight_on == "input", grouping=grouping)
         shared = None if self.shared is None else self.shared.forward(x, ctx)
         return K.moe_combine(pairs, x.shape[0], self.top_k, shared, gates)
 

@@ -232,7 +232,11 @@ def moe_route(x, router, top, *, score="sigmoid", renormalize=False, gate_rows=N
     return ids, weights, gates
 
 
-def moe_experts(x, ids, weights, gate_up, down, *, weight_on_input):
+def moe_path(x, pairs, ff):
+    return "tiles"
+
+
+def moe_experts(x, ids, weights, gate_up, down, *, weight_on_input, path=None, grouping=None):
     tokens, top = ids.shape
     ff = gate_up.shape[1] // 2
     out = torch.empty(tokens * top, down.shape[1], dtype=x.dtype, device=x.device)
@@ -338,7 +342,7 @@ def sample(logits, packed_params, eps):
 _NAMES = [
     "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "feed_tokens", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
-    "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine",
+    "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
 ]
 
 

@@ -88,9 +88,13 @@ def route(h, router_weight, top):
     return ids, values
 
 
-def mixture_ff(h, w, prefix, mlp):
-    """Routed experts fed with ``score * h`` (scores not renormalised) plus a gated shared expert."""
+def mixture_ff(h, w, prefix, mlp, margins=None):
+    """Routed experts fed with ``score * h`` (scores not renormalised) plus a gated shared expert.
+    ``margins`` (a list) receives, per token, the gap between the last chosen and the first unchosen score."""
     ids, scores = route(h, w[f"{prefix}.router"], mlp["router"]["top"])
+    if margins is not None and mlp["router"]["top"] < mlp["router"]["experts"]:
+        ordered = torch.sigmoid(h @ w[f"{prefix}.router"].T).sort(dim=-1, descending=True).values
+        margins.append(ordered[:, mlp["router"]["top"] - 1] - ordered[:, mlp["router"]["top"]])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(ids[t].tolist(), scores[t]):
@@ -101,15 +105,15 @@ def mixture_ff(h, w, prefix, mlp):
     return out
 
 
-def feed_forward(h, w, prefix, mlp):
+def feed_forward(h, w, prefix, mlp, margins=None):
     if mlp["kind"] == "dense":
         return clamped_gated_ff(h, w, prefix, mlp["limit"])
     if mlp["kind"] == "moe":
-        return mixture_ff(h, w, prefix, mlp)
+        return mixture_ff(h, w, prefix, mlp, margins)
     raise ValueError(mlp["kind"])
 
 
-def layer(x, w, index, spec, eps, positions=None):
+def layer(x, w, index, spec, eps, positions=None, margins=None):
     """Both sub-layers read the same stream: ``x + (mixer(norm1 x) + ff(norm2 x))``."""
     prefix = f"l{index}"
     if spec["type"] != "attention":
@@ -118,16 +122,17 @@ def layer(x, w, index, spec, eps, positions=None):
                         spec["mixer"], eps, positions)
     if spec.get("mlp") is None:
         return x + a
-    f = feed_forward(layer_norm_scale_only(x, w[f"{prefix}.norm2"], eps), w, f"{prefix}.mlp", spec["mlp"])
+    f = feed_forward(layer_norm_scale_only(x, w[f"{prefix}.norm2"], eps), w, f"{prefix}.mlp", spec["mlp"], margins)
     return x + (a + f)
 
 
-def forward(cfg, w, tokens, collect=None):
-    """Logits ``[T, vocab]`` of one sequence; ``collect`` (a list) receives the stream after each layer."""
+def forward(cfg, w, tokens, collect=None, margins=None):
+    """Logits ``[T, vocab]`` of one sequence; ``collect`` (a list) receives the stream after each layer,
+    ``margins`` (a list) every mixture layer's per-token gap between chosen and unchosen scores."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for index, spec in enumerate(cfg["layers"]):
-        x = layer(x, w, index, spec, eps)
+        x = layer(x, w, index, spec, eps, margins=margins)
         if collect is not None:
             collect.append(x)
     return layer_norm_scale_only(x, w["final.norm"], eps) @ w["embed"].T

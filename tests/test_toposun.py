@@ -26,7 +26,10 @@ from kvcore_b200.engine.llm_engine import GenerationRequest, LLMEngine
 from kvcore_b200.weights.safetensors_io import write_safetensors
 
 BACKENDS = [pytest.param("cpu", id="host"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
-TOLERANCE = {"float32": 3e-5, "bfloat16": 3e-2}     # largest |difference| over the request's largest |logit|
+# largest |difference| of a row over the request's largest |logit|; in bfloat16 also the root mean square of a
+# row's difference (its mean taken off) over that of the request's logits
+TOLERANCE = {"float32": 3e-5, "bfloat16": 6e-2}
+BF16_RMS_TOLERANCE = 3e-2
 
 
 @pytest.fixture(params=BACKENDS)
@@ -78,16 +81,29 @@ def case(request, tmp_path_factory):
     folder = tmp_path_factory.mktemp(f"toposun_{name}")
     weights = write_folder(folder, cfg, seed=len(name))
     requests = {f"q{i}": rc.random_tokens(cfg["vocab"], n, 30 + i) for i, n in enumerate(LENGTHS[name])}
-    reference = {rid: T.forward(cfg, weights, toks).numpy() for rid, toks in requests.items()}
-    return dict(name=name, cfg=cfg, folder=folder, weights=weights, requests=requests, reference=reference)
+    reference, close_calls = {}, set()
+    for rid, toks in requests.items():
+        margins = []
+        reference[rid] = T.forward(cfg, weights, toks, margins=margins).numpy()
+        # positions where a router's choice hangs on less than bfloat16 keeps apart are not compared in bfloat16
+        for gaps in margins:
+            close_calls.update((rid, int(p)) for p in torch.nonzero(gaps < 2e-2).flatten())
+    return dict(name=name, cfg=cfg, folder=folder, weights=weights, requests=requests, reference=reference,
+                close_calls=close_calls)
 
 
-def compare(rows, reference, dtype):
+def compare(rows, reference, dtype, close_calls=()):
     assert rows
     for (rid, pos), row in sorted(rows.items()):
+        if dtype == "bfloat16" and (rid, pos) in close_calls:
+            continue
         assert np.isfinite(row).all(), f"non-finite logits for {rid}@{pos}"
         err = np.abs(row - reference[rid][pos]).max() / np.abs(reference[rid]).max()
         assert err <= TOLERANCE[dtype], f"{rid}: first wrong position {pos} (error {err:.3e})"
+        if dtype == "bfloat16":
+            diff = row - reference[rid][pos]
+            rms = np.sqrt(np.mean((diff - diff.mean()) ** 2)) / reference[rid].std()
+            assert rms <= BF16_RMS_TOLERANCE, f"{rid}: first wrong position {pos} (rms error {rms:.3e})"
 
 
 # ---- configuration -----------------------------------------------------------------------------------
@@ -169,7 +185,7 @@ def test_cuttings_match_the_plain_statement(case, dtype, device, tmp_path):
                          fill_freed_pages="poison" if name == "mixed" else None)
         rows = rc.collect(steps, out, cfg["vocab"])
         assert len(rows) == sum(len(t) for t in requests.values())
-        compare(rows, case["reference"], dtype)
+        compare(rows, case["reference"], dtype, case["close_calls"])
         results[name] = rows
     if dtype == "float32" and device != "cpu":
         # every kernel of the 32-bit path sums in an order that depends on the position only
@@ -240,7 +256,10 @@ def test_long_decoding_past_windows_and_pages(dtype, device, tmp_path):
 
     step_function, kv = build_replay(str(folder), dtype, 112, device=device, fill_freed_pages="poison", max_model_len=256)
     rc.run_on(step_function, kv, steps, out)
-    compare(rc.collect(steps, out, cfg["vocab"]), {"a": T.forward(cfg, weights, tokens).numpy()}, dtype)
+    margins = []
+    reference = {"a": T.forward(cfg, weights, tokens, margins=margins).numpy()}
+    close_calls = {("a", int(p)) for gaps in margins for p in torch.nonzero(gaps < 2e-2).flatten()}
+    compare(rc.collect(steps, out, cfg["vocab"]), reference, dtype, close_calls)
 
 
 def test_each_mechanism_changes_the_logits(tmp_path):

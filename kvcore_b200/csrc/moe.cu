@@ -366,6 +366,123 @@ extern "C" int kvb_moe_gemv(void* out, const void* a, long long a_stride, int a_
   return 0;
 }
 
+// The same for a few hundred pairs: the pairs of one expert share one pass over its matrices.  grid (N / 32,
+// 2 * tiles): a block takes one half (8 rows) of a tile of the grouped order (moe_align), holds those pairs'
+// input rows in shared memory and gives each warp 4 output columns (GATED: 4 gate and 4 up rows) for all
+// 8 rows; a weight vector is loaded once and used for every row.
+#define MOE_GEMV_ROWS 8
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemv_rows_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, long long a_stride, int a_row_div,
+                     const float* __restrict__ pair_weight, const bf16* __restrict__ w,
+                     const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                     const int* __restrict__ meta, int N, int K) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_GEMM);
+  extern __shared__ __align__(16) unsigned char gemv_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(gemv_smem);            // [MOE_GEMV_ROWS][K]
+  __shared__ int pair_of[MOE_GEMV_ROWS];
+  const int tile = blockIdx.y >> 1, half = blockIdx.y & 1;
+  if (tile >= meta[0]) return;
+  const int first = sorted[tile * MOE_BM + half * MOE_GEMV_ROWS];
+  if (first < 0) return;                                     // a run fills its tiles from the front
+  if (threadIdx.x < MOE_GEMV_ROWS) pair_of[threadIdx.x] = sorted[tile * MOE_BM + half * MOE_GEMV_ROWS + threadIdx.x];
+  __syncthreads();
+  const int expert = tile_expert[tile];
+  for (int i = threadIdx.x * 8; i < MOE_GEMV_ROWS * K; i += 256 * 8) {
+    const int r = i / K, k = i % K;
+    const int pair = pair_of[r];
+    Vec16<bf16> v;
+    if (pair >= 0) {
+      v.load(a + (size_t)(pair / a_row_div) * a_stride + k);
+      if (pair_weight != nullptr) {
+        const float scale = pair_weight[pair];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v.set(j, v.get(j) * scale);
+      }
+    } else {
+      v.raw = make_uint4(0, 0, 0, 0);
+    }
+    v.store(xs + i);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * MOE_GEMV_COLS + warp * 4;
+  const bf16* we = w + (size_t)expert * (GATED ? 2 : 1) * N * K;
+  constexpr int COLS = GATED ? 8 : 4;
+  const bf16* cols[COLS];
+  float acc[COLS][MOE_GEMV_ROWS];
+#pragma unroll
+  for (int c = 0; c < COLS; ++c) {
+    const int n = min(n0 + (c & 3), N - 1) + (c >= 4 ? N : 0);
+    cols[c] = we + (size_t)n * K;
+#pragma unroll
+    for (int r = 0; r < MOE_GEMV_ROWS; ++r) acc[c][r] = 0.0f;
+  }
+  for (int k = lane * 8; k < K; k += 32 * 8) {
+    Vec16<bf16> wv[COLS];
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) wv[c].load(cols[c] + k);
+#pragma unroll
+    for (int r = 0; r < MOE_GEMV_ROWS; ++r) {
+      Vec16<bf16> x;
+      x.load(xs + (size_t)r * K + k);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xv = x.get(j);
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) acc[c][r] = fmaf(wv[c].get(j), xv, acc[c][r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < COLS; ++c)
+#pragma unroll
+    for (int r = 0; r < MOE_GEMV_ROWS; ++r) acc[c][r] = warp_sum(acc[c][r]);
+  // lane (r, c) = (lane / 4, lane % 4) writes one output
+  const int r = lane >> 2, c = lane & 3;
+  float v = 0.0f, u = 0.0f;
+#pragma unroll
+  for (int rr = 0; rr < MOE_GEMV_ROWS; ++rr)
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc)
+      if (rr == r && cc == c) {
+        v = acc[cc][rr];
+        if (GATED) u = acc[(cc + 4) % COLS][rr];
+      }
+  const int pair = pair_of[r];
+  if (pair >= 0 && n0 + c < N) {
+    if (GATED) {
+      const float g = to_float(from_float<bf16>(v));
+      v = to_float(from_float<bf16>(moe_silu<bf16>(g))) * to_float(from_float<bf16>(u));
+    }
+    out[(size_t)pair * N + n0 + c] = from_float<bf16>(v);
+  }
+}
+
+extern "C" int kvb_moe_gemv_rows(void* out, const void* a, long long a_stride, int a_row_div, const float* pair_weight,
+                                 const void* w, const int* sorted, const int* tile_expert, const int* meta,
+                                 int max_tiles, int N, int K, int gated, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  KVB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && a_stride % 8 == 0 && a_row_div > 0, "moe_gemv_rows: K and the row stride must be multiples of 8");
+  KVB_REQUIRE(aligned16(a) && aligned16(w), "moe_gemv_rows: operands must be 16-byte aligned");
+  KVB_REQUIRE(2 * (long long)max_tiles <= 65535, "moe_gemv_rows: too many tiles for one launch");
+  const size_t smem = (size_t)MOE_GEMV_ROWS * K * sizeof(bf16);
+  KVB_REQUIRE(smem <= 200 * 1024, "moe_gemv_rows: the input rows do not fit in shared memory");
+  dim3 grid((N + MOE_GEMV_COLS - 1) / MOE_GEMV_COLS, 2 * max_tiles);
+#define KVB_MOE_GEMV_ROWS(G_)                                                                                 \
+  do {                                                                                                        \
+    if (smem > 48 * 1024)                                                                                     \
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(moe_gemv_rows_kernel<G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    KVB_CHECK_CUDA(kvb_launch((moe_gemv_rows_kernel<G_>), grid, dim3(256), smem, stream, true, (bf16*)out,     \
+                              (const bf16*)a, a_stride, a_row_div, pair_weight, (const bf16*)w, sorted,        \
+                              tile_expert, meta, N, K));                                                       \
+  } while (0)
+  if (gated) KVB_MOE_GEMV_ROWS(true); else KVB_MOE_GEMV_ROWS(false);
+#undef KVB_MOE_GEMV_ROWS
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
 // Rows in the grouped order for batched library products: expert e owns rows [e * C, (e + 1) * C) of `out`;
 // row e * C + j holds weight(p) * a[p / a_row_div] for the j-th pair p of the expert (sorted[expert_begin[e] + j]),
 // zeros beyond the expert's pairs.  row_of_pair[p] is set to the row that pair p got.

@@ -54,6 +54,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_moe_route": [_vp, _vp, _vp, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _vp],
         "kvb_moe_align": [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _vp],
         "kvb_moe_gemv": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_moe_gemv_rows": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _vp],
         "kvb_moe_gather": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _int, _int, _vp, _int, _int, _vp],
         "kvb_moe_gemm": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
         "kvb_moe_combine": [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _int, _int, _int, _vp],
@@ -1022,7 +1023,10 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, score: str = "
 
 # bf16 batches of at most this many (token, expert) pairs take the kernel that streams each chosen expert's
 # matrices once; larger ones take library products over each expert's run of rows
-MOE_GEMV_MAX_PAIRS = int(os.environ.get("KVCORE_B200_MOE_GEMV_PAIRS", "256"))
+MOE_GEMV_MAX_PAIRS = int(os.environ.get("KVCORE_B200_MOE_GEMV_PAIRS", "512"))
+# up to this many pairs, or fewer than four pairs an expert, each pair streams its expert alone; otherwise
+# the pairs are grouped by expert first
+MOE_GEMV_SINGLE_PAIRS = int(os.environ.get("KVCORE_B200_MOE_GEMV_SINGLE_PAIRS", "16"))
 
 
 class ExpertRows:
@@ -1116,6 +1120,18 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_
     code = _dtype_code(x)
     if path is None:
         path = moe_path(x, pairs, ff)
+    if path == "stream" and pairs > MOE_GEMV_SINGLE_PAIRS and pairs >= 4 * experts:
+        # enough pairs that experts are shared: the pairs of an expert take one pass over its matrices together
+        g = grouping if grouping is not None else moe_group(ids, experts, for_library=False)
+        hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+        _call("kvb_moe_gemv_rows", hidden.data_ptr(), x.data_ptr(), x.stride(0), top,
+              weights.data_ptr() if weight_on_input else None, gate_up.data_ptr(), g.sorted_pairs.data_ptr(),
+              g.tile_expert.data_ptr(), g.meta.data_ptr(), g.max_tiles, ff, k, 1, _stream())
+        out = torch.empty((pairs, n), dtype=x.dtype, device=x.device)
+        _call("kvb_moe_gemv_rows", out.data_ptr(), hidden.data_ptr(), hidden.stride(0), 1,
+              None if weight_on_input else weights.data_ptr(), down.data_ptr(), g.sorted_pairs.data_ptr(),
+              g.tile_expert.data_ptr(), g.meta.data_ptr(), g.max_tiles, n, ff, 0, _stream())
+        return ExpertRows(out)
     if path == "stream":
         hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
         _call("kvb_moe_gemv", hidden.data_ptr(), x.data_ptr(), x.stride(0), top,
@@ -1135,14 +1151,16 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_
     max_tiles, capacity = grouping.max_tiles, grouping.capacity
     if library:
         begins = grouping.begins()                # the one read-back: how many rows each expert got
-        stride = max(begins[e + 1] - begins[e] for e in range(experts))    # a multiple of the tile's rows
+        # the common stride: the fullest expert's rows, rounded up to 64 so that the library sees few
+        # different shapes (it chooses a kernel anew for every shape it has not met: about a millisecond)
+        stride = -(-max(begins[e + 1] - begins[e] for e in range(experts)) // 64) * 64
         gathered = torch.empty((experts, stride, k), dtype=x.dtype, device=x.device)
         _call("kvb_moe_gather", gathered.data_ptr(), x.data_ptr(), x.stride(0), top,
               weights.data_ptr() if weight_on_input else None, sorted_pairs.data_ptr(), expert_begin.data_ptr(),
               experts, stride, row_of_pair.data_ptr(), k, code, _stream())
         # every expert's rows at one stride: two batched library products over all experts (an expert with
         # fewer pairs multiplies zero rows; with one expert far fuller than the rest, expert by expert instead)
-        if experts * stride <= 2 * capacity + experts * tile:
+        if experts * stride <= 2 * capacity + experts * 64:
             both = torch.bmm(gathered, gate_up.transpose(1, 2))
             hidden = silu_mul(both.view(experts * stride, two_ff), 0).view(experts, stride, ff)
             out = torch.bmm(hidden, down.transpose(1, 2)).view(experts * stride, n)

@@ -126,7 +126,7 @@ def test_moe_route_takes_the_lowest_index_among_equal_scores():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,experts,top,width,ff,on_input", [
     (5, 12, 1, 256, 96, True), (40, 4, 2, 96, 40, True), (3, 7, 3, 64, 130, False), (70, 3, 1, 200, 64, True),
-    (1, 2, 2, 32, 8, True)])
+    (1, 2, 2, 32, 8, True), (64, 32, 4, 256, 96, True), (30, 5, 2, 128, 40, False)])
 def test_moe_experts_and_combine(dtype, tokens, experts, top, width, ff, on_input):
     x = randn(tokens, width, dtype=dtype, seed=1)
     gate_up = randn(experts, 2 * ff, width, dtype=dtype, seed=2, scale=0.2)

@@ -3,8 +3,8 @@
 // A windowed attention kernel leaves, per (token, head), its normalised output and
 //   lse = log2( sum over the window's keys of 2^(score * scale * log2 e) ).
 // A query at position p with window w and `keep_first` kept positions also sees the keys
-// j < min(keep_first, p - w + 1): those behind its window.  One warp per (token, head) scores them one
-// after the other (the lanes spread over the head, 32-bit, online maximum and sum in the same base-2
+// j < min(keep_first, p - w + 1): those behind its window.  One warp per (token, head) scores them four
+// at a time (the lanes spread over the head, 32-bit, online maximum and sum in the same base-2
 // domain) and merges:
 //   out = (out_w * 2^(lse - M) + sum_j 2^(s_j - M) v_j) / (2^(lse - M) + sum_j 2^(s_j - M)),  M = max(lse, max_j s_j).
 // Rows whose window reaches back into the kept positions have nothing to add and are left as they are.
@@ -45,26 +45,56 @@ kept_first_merge_kernel(T* __restrict__ out, int out_stride, const float* __rest
   float running_max = -INFINITY, running_sum = 0.0f;
   const size_t head_off = (size_t)kvh * page_size * D;
   const size_t page_elems = (size_t)KVH * page_size * D;
-  // one key at a time, the lanes spread over the head: every load is a coalesced row of the cache
-  for (int key = 0; key < kept; ++key) {
-    const int page = pages[key / page_size];
-    if (page <= 0 || page >= num_pages) {
-      if (lane == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
-      continue;
+  // four keys at a time, the lanes spread over the head: every load is a coalesced row of the cache and
+  // the four keys' loads and sums are independent of each other
+  for (int key0 = 0; key0 < kept; key0 += 4) {
+    size_t at[4];
+    float dot[4];
+    bool live[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int key = key0 + i;
+      live[i] = key < kept;
+      const int page = live[i] ? pages[key / page_size] : 0;
+      if (live[i] && (page <= 0 || page >= num_pages)) {
+        if (lane == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+        live[i] = false;
+      }
+      at[i] = (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
+      dot[i] = 0.0f;
     }
-    const size_t at = (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
-    float dot = 0.0f;
-    for (int d = lane; d < D; d += 32) dot = fmaf(to_float(k_cache[at + d]), q_smem[warp][d], dot);
-    const float score = warp_sum(dot) * scale_log2;
-    const float new_max = fmaxf(running_max, score);
-    const float p = exp2f(score - new_max);
+    for (int d = lane; d < D; d += 32) {
+      const float qd = q_smem[warp][d];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (live[i]) dot[i] = fmaf(to_float(k_cache[at[i] + d]), qd, dot[i]);
+    }
+    float score[4], new_max = running_max;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      score[i] = live[i] ? warp_sum(dot[i]) * scale_log2 : -INFINITY;
+      new_max = fmaxf(new_max, score[i]);
+    }
+    if (new_max == -INFINITY) continue;
     const float correction = (running_max == -INFINITY) ? 0.0f : exp2f(running_max - new_max);
-    running_sum = running_sum * correction + p;
+    float p[4];
+    running_sum *= correction;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[i] = live[i] ? exp2f(score[i] - new_max) : 0.0f;
+      running_sum += p[i];
+    }
     running_max = new_max;
 #pragma unroll
-    for (int i = 0; i < SLICES; ++i) {
-      const int d = lane + 32 * i;
-      if (d < D) acc[i] = fmaf(p, to_float(v_cache[at + d]), acc[i] * correction);
+    for (int s = 0; s < SLICES; ++s) {
+      const int d = lane + 32 * s;
+      if (d < D) {
+        float v = acc[s] * correction;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (live[i]) v = fmaf(p[i], to_float(v_cache[at[i] + d]), v);
+        acc[s] = v;
+      }
     }
   }
   if (!(running_sum > 0.0f)) return;

@@ -1,7 +1,7 @@
 // Mixture of experts: router, grouping of (token, chosen expert) pairs by expert, the experts' two
 // matrix products as grouped products over that order, and the weighted sum back per token.
 //
-//   route:   z = W_router x in 32-bit (one warp per expert row, lane-strided ascending k, butterfly sum);
+//   route:   z = W_router x in 32-bit (one warp per expert row, lane-strided k in a fixed order, butterfly sum);
 //            scores = sigmoid(z) or softmax(z); the `top` largest (lowest index among equals); weights are
 //            the chosen scores, optionally divided by their sum.  Extra rows (a shared expert's gate) are
 //            dotted the same way and leave sigmoid(row . x).
@@ -25,43 +25,77 @@
 #define MOE_BM 16
 #define MOE_BN 64
 #define MOE_BK 16
-#define MOE_ROUTE_THREADS 128
+#define MOE_ROUTE_THREADS 512
 
-template <typename T>
+// TPB tokens a block share every pass over a router row (a prompt's tokens would otherwise each pull the
+// whole router through the L2 cache); a token's sums are formed in the same order whatever TPB is: lane l
+// adds the products k = l, l + 32, ... into four partial sums by (k / 32) % 4, then ((p0 + p1) + (p2 + p3)),
+// then the butterfly over the lanes.
+template <typename T, int TPB>
 __global__ void __launch_bounds__(MOE_ROUTE_THREADS)
 moe_route_kernel(int* __restrict__ ids_out, float* __restrict__ weights_out, float* __restrict__ gate_out,
                  const T* __restrict__ x, long long x_stride, const float* __restrict__ router,
-                 const float* __restrict__ gate_rows, int E, int R, int K, int top, int score_mode,
+                 const float* __restrict__ gate_rows, int tokens, int E, int R, int K, int top, int score_mode,
                  int renormalize) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_ROUTE);
-  extern __shared__ float smem[];
-  float* xs = smem;          // [K]
-  float* scores = smem + K;  // [E + R]
-  const int token = blockIdx.x;
+  extern __shared__ __align__(16) unsigned char route_smem[];
+  T* xs = reinterpret_cast<T*>(route_smem);                                   // [TPB][K]
+  float* scores = reinterpret_cast<float*>(route_smem + (size_t)TPB * K * sizeof(T));   // [TPB][E + R]
+  const int token0 = blockIdx.x * TPB;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = MOE_ROUTE_THREADS / 32;
-  const T* row = x + (size_t)token * x_stride;
-  for (int k = threadIdx.x; k < K; k += MOE_ROUTE_THREADS) xs[k] = to_float(row[k]);
+  for (int i = threadIdx.x; i < TPB * K; i += MOE_ROUTE_THREADS) {
+    const int t = i / K, k = i % K;
+    xs[i] = token0 + t < tokens ? x[(size_t)(token0 + t) * x_stride + k] : from_float<T>(0.0f);
+  }
   __syncthreads();
   for (int e = warp; e < E + R; e += nwarps) {
     const float* w = e < E ? router + (size_t)e * K : gate_rows + (size_t)(e - E) * K;
-    float acc = 0.0f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(w[k], xs[k], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) scores[e] = acc;
+    float part[TPB][4];
+#pragma unroll
+    for (int t = 0; t < TPB; ++t) part[t][0] = part[t][1] = part[t][2] = part[t][3] = 0.0f;
+    int k = lane;
+    for (; k + 96 < K; k += 128) {
+      const float w0 = w[k], w1 = w[k + 32], w2 = w[k + 64], w3 = w[k + 96];
+#pragma unroll
+      for (int t = 0; t < TPB; ++t) {
+        const T* xt = xs + (size_t)t * K;
+        part[t][0] = fmaf(w0, to_float(xt[k]), part[t][0]);
+        part[t][1] = fmaf(w1, to_float(xt[k + 32]), part[t][1]);
+        part[t][2] = fmaf(w2, to_float(xt[k + 64]), part[t][2]);
+        part[t][3] = fmaf(w3, to_float(xt[k + 96]), part[t][3]);
+      }
+    }
+    for (int j = 0; k < K; k += 32, ++j) {
+      const float wk = w[k];
+#pragma unroll
+      for (int t = 0; t < TPB; ++t) {
+        const float prod_x = to_float(xs[(size_t)t * K + k]);
+        if (j == 0) part[t][0] = fmaf(wk, prod_x, part[t][0]);
+        else if (j == 1) part[t][1] = fmaf(wk, prod_x, part[t][1]);
+        else part[t][2] = fmaf(wk, prod_x, part[t][2]);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TPB; ++t) {
+      const float acc = warp_sum((part[t][0] + part[t][1]) + (part[t][2] + part[t][3]));
+      if (lane == 0) scores[t * (E + R) + e] = acc;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
-  for (int r = lane; r < R; r += 32) gate_out[(size_t)token * R + r] = 1.0f / (1.0f + expf(-scores[E + r]));
+  if (warp >= TPB || token0 + warp >= tokens) return;
+  const int token = token0 + warp;                    // warp t finishes token t of the block
+  float* sc = scores + warp * (E + R);
+  for (int r = lane; r < R; r += 32) gate_out[(size_t)token * R + r] = 1.0f / (1.0f + expf(-sc[E + r]));
   if (score_mode == 0) {
-    for (int e = lane; e < E; e += 32) scores[e] = 1.0f / (1.0f + expf(-scores[e]));
+    for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
   } else {
     float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, scores[e]);
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
     m = warp_max(m);
-    float s = 0.0f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(scores[e] - m); scores[e] = p; s += p; }
-    s = warp_sum(s);
-    for (int e = lane; e < E; e += 32) scores[e] = scores[e] / s;
+    float sum = 0.0f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
   }
   __syncwarp();
   float chosen_sum = 0.0f;
@@ -69,7 +103,7 @@ moe_route_kernel(int* __restrict__ ids_out, float* __restrict__ weights_out, flo
     float best = -INFINITY;
     int best_e = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float v = scores[e];
+      const float v = sc[e];
       if (v > best) { best = v; best_e = e; }   // ascending e: the lowest index among equals stays
     }
 #pragma unroll
@@ -81,13 +115,27 @@ moe_route_kernel(int* __restrict__ ids_out, float* __restrict__ weights_out, flo
     if (lane == 0) {
       ids_out[(size_t)token * top + slot] = best_e;
       weights_out[(size_t)token * top + slot] = best;
-      scores[best_e] = -INFINITY;
+      sc[best_e] = -INFINITY;
     }
     chosen_sum += best;
     __syncwarp();
   }
   if (renormalize && lane == 0)
     for (int slot = 0; slot < top; ++slot) weights_out[(size_t)token * top + slot] /= chosen_sum;
+}
+
+template <typename T, int TPB>
+static int launch_moe_route(int* ids_out, float* weights_out, float* gate_out, const void* x, long long x_stride,
+                            const float* router, const float* gate_rows, int tokens, int E, int R, int K, int top,
+                            int score_mode, int renormalize, cudaStream_t stream) {
+  const size_t smem = (size_t)TPB * K * sizeof(T) + (size_t)TPB * (E + R) * sizeof(float);
+  KVB_REQUIRE(smem <= 200 * 1024, "moe_route: the tokens' rows and scores do not fit in shared memory");
+  if (smem > 48 * 1024)
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(moe_route_kernel<T, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  KVB_CHECK_CUDA(kvb_launch((moe_route_kernel<T, TPB>), dim3((tokens + TPB - 1) / TPB), dim3(MOE_ROUTE_THREADS), smem,
+                            stream, true, ids_out, weights_out, gate_out, (const T*)x, x_stride, router, gate_rows,
+                            tokens, E, R, K, top, score_mode, renormalize));
+  return 0;
 }
 
 extern "C" int kvb_moe_route(int* ids_out, float* weights_out, float* gate_out, const void* x, long long x_stride,
@@ -97,18 +145,16 @@ extern "C" int kvb_moe_route(int* ids_out, float* weights_out, float* gate_out, 
   KVB_REQUIRE(E > 0 && K > 0 && top > 0 && top <= E, "moe_route: need 0 < top <= experts");
   KVB_REQUIRE(R >= 0 && (R == 0 || (gate_rows != nullptr && gate_out != nullptr)), "moe_route: gate rows need their weights and output");
   KVB_REQUIRE(score_mode == 0 || score_mode == 1, "moe_route: unknown score function");
-  const size_t smem = (size_t)(K + E + R) * sizeof(float);
-  KVB_REQUIRE(smem <= 200 * 1024, "moe_route: a token's row and scores do not fit in shared memory");
-#define KVB_ROUTE(T_)                                                                                          \
-  do {                                                                                                         \
-    if (smem > 48 * 1024)                                                                                      \
-      KVB_CHECK_CUDA(cudaFuncSetAttribute(moe_route_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    KVB_CHECK_CUDA(kvb_launch((moe_route_kernel<T_>), dim3(tokens), dim3(MOE_ROUTE_THREADS), smem, stream, true, \
-                              ids_out, weights_out, gate_out, (const T_*)x, x_stride, router, gate_rows, E, R, K, \
-                              top, score_mode, renormalize));                                                  \
-  } while (0)
-  if (dtype == KVB_F32) KVB_ROUTE(float); else KVB_ROUTE(bf16);
-#undef KVB_ROUTE
+  // a prompt's tokens go eight a block; a few tokens one a block, for the parallelism
+  const bool many = tokens >= 256 && (size_t)8 * K * (dtype == KVB_F32 ? 4 : 2) <= 96 * 1024;
+  int rc;
+  if (dtype == KVB_F32)
+    rc = many ? launch_moe_route<float, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream)
+              : launch_moe_route<float, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream);
+  else
+    rc = many ? launch_moe_route<bf16, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream)
+              : launch_moe_route<bf16, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream);
+  if (rc) return rc;
   KVB_CHECK_LAUNCH();
   return 0;
 }

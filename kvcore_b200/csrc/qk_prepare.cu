@@ -17,6 +17,9 @@
 #include "common.cuh"
 
 #define QKP_THREADS 256
+// where element i of the token's projections lies in shared memory: one pad after every 32 floats, so that
+// threads that each hold 8 neighbouring elements fall into different banks
+#define QKP_AT(i) ((i) + ((i) >> 5))
 
 template <typename T, typename W>
 __global__ void __launch_bounds__(QKP_THREADS)
@@ -29,9 +32,8 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   KVB_KERNEL_PROLOGUE(KVB_TAG_QK_PREPARE);
   extern __shared__ float smem[];
   const int heads = H + KVH;
-  float* x = smem;                       // [heads * D]: q heads then k heads, 32-bit
-  float* head_sq = smem + (size_t)heads * D;   // [heads]
-  float* inv = head_sq + heads;          // [heads]
+  float* x = smem;                       // [heads * D] (+ one pad after every 32): q heads then k heads, 32-bit
+  float* head_sq = smem + QKP_AT((size_t)heads * D) + 1;   // [heads]
   const int token = blockIdx.x;
   const int pos = positions[token];
   T* row = rows + (size_t)token * row_stride;
@@ -43,10 +45,10 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
       Vec16<T> v;
       v.load(row + i);
 #pragma unroll
-      for (int j = 0; j < VN; ++j) x[i + j] = v.get(j);
+      for (int j = 0; j < VN; ++j) x[QKP_AT(i + j)] = v.get(j);
     }
   } else {
-    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[QKP_AT(i)] = to_float(row[i]);
   }
   __syncthreads();
 
@@ -81,63 +83,71 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   if (norm_mode != 0) {
     for (int h = warp; h < heads; h += nwarps) {
       float sq = 0.0f;
-      for (int d = lane; d < D; d += 32) { const float v = x[(size_t)h * D + d]; sq = fmaf(v, v, sq); }
+      for (int d = lane; d < D; d += 32) { const float v = x[QKP_AT(h * D + d)]; sq = fmaf(v, v, sq); }
       sq = warp_sum(sq);
       if (lane == 0) head_sq[h] = sq;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      if (norm_mode == 1) {
-        float q_sq = 0.0f, k_sq = 0.0f;
-        for (int h = 0; h < H; ++h) q_sq += head_sq[h];
-        for (int h = H; h < heads; ++h) k_sq += head_sq[h];
-        const float q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
-        const float k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
-        for (int h = 0; h < heads; ++h) inv[h] = h < H ? q_inv : k_inv;
-      } else {
-        for (int h = 0; h < heads; ++h) inv[h] = 1.0f / sqrtf(head_sq[h] / (float)D + eps);
-      }
+    // every thread forms the scales itself, adding the heads' sums in ascending order
+    float q_inv = 0.0f, k_inv = 0.0f;
+    if (norm_mode == 1) {
+      float q_sq = 0.0f, k_sq = 0.0f;
+      for (int h = 0; h < H; ++h) q_sq += head_sq[h];
+      for (int h = H; h < heads; ++h) k_sq += head_sq[h];
+      q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
+      k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
-      const int h = i / D, d = i % D;
-      float w;
-      if (norm_mode == 1) w = h < H ? to_float(q_weight[i]) : to_float(k_weight[i - H * D]);
-      else w = h < H ? to_float(q_weight[d]) : to_float(k_weight[d]);
-      x[i] = x[i] * inv[h] * w;
+    const int step = vec ? VN : 1;
+    for (int i = threadIdx.x * step; i < heads * D; i += QKP_THREADS * step) {
+      const int h = i / D, d = i % D;       // a vector never crosses a head: D is a multiple of its length
+      const float scale = norm_mode == 1 ? (h < H ? q_inv : k_inv) : 1.0f / sqrtf(head_sq[h] / (float)D + eps);
+      const W* w = norm_mode == 1 ? (h < H ? q_weight + i : k_weight + (i - H * D)) : (h < H ? q_weight + d : k_weight + d);
+#pragma unroll
+      for (int j = 0; j < VN; ++j)
+        if (j < step) x[QKP_AT(i + j)] = x[QKP_AT(i + j)] * scale * to_float(w[j]);
     }
     __syncthreads();
   }
 
   const int half = rot >> 1;
-  if (cos_sin != nullptr && half > 0) {
-    for (int item = threadIdx.x; item < heads * half; item += QKP_THREADS) {
-      const int h = item / half, j = item % half;
-      const float2 cs = cos_sin[(size_t)token * half + j];
-      float* p = x + (size_t)h * D;
-      const float a = p[j], b = p[j + half];
-      p[j] = a * cs.x - b * cs.y;
-      p[j + half] = b * cs.x + a * cs.y;
-    }
-    __syncthreads();
-  }
-
-  __syncthreads();   // the values were copied from the row that is overwritten now
-  if (vec) {
+  const bool turn = cos_sin != nullptr && half > 0;
+  __syncthreads();   // the values were copied from the row that is overwritten from here on
+  if (vec && (!turn || half % VN == 0)) {
+    // rotation and store in one pass: a vector of the turned part takes its partner vector from shared memory
     for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+      const int h = i / D, d = i % D;
       Vec16<T> v;
+      if (turn && d < rot) {
+        const bool low = d < half;
+        const int mate = low ? i + half : i - half;
+        const float2* cs = cos_sin + (size_t)token * half + (low ? d : d - half);
 #pragma unroll
-      for (int j = 0; j < VN; ++j) v.set(j, x[i + j]);
-      v.store(row + i);
-      if (i >= H * D && write) {
-        const int kh = (i - H * D) / D, d = (i - H * D) % D;
-        v.store(k_cache + cache_base + (size_t)kh * head_stride + d);
+        for (int j = 0; j < VN; ++j) {
+          const float2 t = cs[j];
+          v.set(j, low ? x[QKP_AT(i + j)] * t.x - x[QKP_AT(mate + j)] * t.y : x[QKP_AT(i + j)] * t.x + x[QKP_AT(mate + j)] * t.y);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VN; ++j) v.set(j, x[QKP_AT(i + j)]);
       }
+      v.store(row + i);
+      if (h >= H && write) v.store(k_cache + cache_base + (size_t)(h - H) * head_stride + d);
     }
     return;
   }
+  if (turn) {
+    for (int item = threadIdx.x; item < heads * half; item += QKP_THREADS) {
+      const int h = item / half, j = item % half;
+      const float2 cs = cos_sin[(size_t)token * half + j];
+      const int lo = h * D + j, hi = lo + half;
+      const float a = x[QKP_AT(lo)], b = x[QKP_AT(hi)];
+      x[QKP_AT(lo)] = a * cs.x - b * cs.y;
+      x[QKP_AT(hi)] = b * cs.x + a * cs.y;
+    }
+    __syncthreads();
+  }
   for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
-    const T v = from_float<T>(x[i]);
+    const T v = from_float<T>(x[QKP_AT(i)]);
     row[i] = v;
     if (i >= H * D && write) {
       const int kh = (i - H * D) / D, d = (i - H * D) % D;
@@ -163,7 +173,8 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   KVB_REQUIRE(row_stride >= needed, "qk_prepare: row stride is smaller than the row");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "qk_prepare: no status word");
-  const size_t smem = ((size_t)(H + KVH) * D + 2 * (size_t)(H + KVH)) * sizeof(float);
+  const size_t elems = (size_t)(H + KVH) * D;
+  const size_t smem = (QKP_AT(elems) + 1 + (size_t)(H + KVH)) * sizeof(float);
   KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
   const int esize = dtype == KVB_F32 ? 4 : 2;
   const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&

@@ -52,7 +52,7 @@ def test_stream_add(dtype):
 QK_CASES = [
     # heads, kv_heads, dim, rotated, norm, keys as values, page
     (4, 2, 16, 8, "projection", True, 16),
-    (6, 1, 128, 64, "projection", True, 16),
+    (10, 2, 128, 96, "projection", True, 16),
     (3, 3, 48, 48, "head", False, 8),
     (5, 1, 80, 0, None, True, 4),
     (8, 2, 64, 32, None, False, 16),
@@ -99,7 +99,7 @@ def test_glu_clamped(dtype, rows, inter, limit):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,experts,top,width,score,renorm,gates", [
-    (7, 12, 1, 256, "sigmoid", False, 1), (33, 5, 3, 96, "sigmoid", True, 0), (4, 64, 8, 520, "softmax", True, 2),
+    (7, 10, 2, 192, "sigmoid", False, 1), (33, 5, 3, 96, "sigmoid", True, 0), (4, 64, 8, 520, "softmax", True, 2),
     (1, 3, 3, 40, "sigmoid", False, 0)])
 def test_moe_route(dtype, tokens, experts, top, width, score, renorm, gates):
     x = randn(tokens, width, dtype=dtype, seed=1)
@@ -125,7 +125,7 @@ def test_moe_route_takes_the_lowest_index_among_equal_scores():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,experts,top,width,ff,on_input", [
-    (5, 12, 1, 256, 96, True), (40, 4, 2, 96, 40, True), (3, 7, 3, 64, 130, False), (70, 3, 1, 200, 64, True),
+    (5, 10, 1, 192, 72, True), (40, 4, 2, 96, 40, True), (3, 7, 3, 64, 130, False), (70, 3, 1, 200, 64, True),
     (1, 2, 2, 32, 8, True), (64, 32, 4, 256, 96, True), (30, 5, 2, 128, 40, False)])
 def test_moe_experts_and_combine(dtype, tokens, experts, top, width, ff, on_input):
     x = randn(tokens, width, dtype=dtype, seed=1)
@@ -181,16 +181,16 @@ class _HostCtx(_Ctx):
 KEPT_FIRST_SHAPES = [
     # dtype, heads, kv_heads, dim, page, [(context, query)], window, kept, what runs
     (torch.float32, 4, 2, 16, 16, [(0, 70), (90, 1), (5, 13)], 24, 5, dict()),
-    (torch.float32, 6, 1, 128, 16, [(0, 300), (299, 1)], 136, 20, dict()),
+    (torch.float32, 10, 2, 128, 16, [(0, 300), (299, 1)], 120, 12, dict()),
     (torch.bfloat16, 3, 1, 40, 8, [(0, 90), (89, 1)], 17, 3, dict()),                       # general kernel: D not of 16
-    (torch.bfloat16, 6, 1, 128, 16, [(0, 300), (100, 150)], 136, 20, dict()),                 # tcgen05 prefill
-    (torch.bfloat16, 6, 1, 128, 16, [(0, 300)], 136, 20, dict(use_tc5=False)),                # mma.sync tiles
-    (torch.bfloat16, 6, 1, 128, 16, [(299, 1), (135, 1), (136, 1), (155, 1), (3, 1), (1500, 1)], 136, 20, dict()),  # TMA decode
-    (torch.bfloat16, 6, 1, 128, 16, [(700, 1), (140, 2)], 136, 20, dict(num_splits=3)),       # TMA decode, splits
+    (torch.bfloat16, 10, 2, 128, 16, [(0, 300), (100, 150)], 120, 12, dict()),                # tcgen05 prefill
+    (torch.bfloat16, 10, 2, 128, 16, [(0, 300)], 120, 12, dict(use_tc5=False)),               # mma.sync tiles
+    (torch.bfloat16, 10, 2, 128, 16, [(299, 1), (119, 1), (120, 1), (131, 1), (3, 1), (1500, 1)], 120, 12, dict()),  # TMA decode
+    (torch.bfloat16, 10, 2, 128, 16, [(700, 1), (140, 2)], 120, 12, dict(num_splits=3)),      # TMA decode, splits
     (torch.bfloat16, 8, 2, 96, 16, [(700, 1), (140, 1), (20, 1)], 100, 33, dict()),           # mma.sync split shape
     (torch.bfloat16, 8, 2, 96, 16, [(700, 1), (140, 1)], 100, 33, dict(num_splits=4)),
     (torch.bfloat16, 4, 4, 64, 32, [(0, 200), (64, 3)], 50, 64, dict()),                      # more kept than the window holds
-    (torch.bfloat16, 6, 1, 128, 16, [(10, 200), (400, 1), (157, 1), (30, 2)], 136, 20, dict()),  # mixed: two kernels, one result
+    (torch.bfloat16, 10, 2, 128, 16, [(10, 200), (400, 1), (133, 1), (30, 2)], 120, 12, dict()),  # mixed: two kernels, one result
 ]
 
 

@@ -17,9 +17,25 @@
 #include "common.cuh"
 
 #define QKP_THREADS 256
-// where element i of the token's projections lies in shared memory: one pad after every 32 floats, so that
-// threads that each hold 8 neighbouring elements fall into different banks
-#define QKP_AT(i) ((i) + ((i) >> 5))
+// where element i of the token's projections lies in shared memory: four pads after every 32 floats, so that
+// threads that each hold 8 neighbouring elements fall into different banks and groups of 4 stay 16-byte aligned
+#define QKP_AT(i) ((i) + (((i) >> 5) << 2))
+
+// 8 (or 4) neighbouring 32-bit values of shared memory as 16-byte accesses
+template <int N>
+__device__ __forceinline__ void qkp_load(float* dst, const float* src) {
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q) {
+    const float4 v = *reinterpret_cast<const float4*>(src + 4 * q);
+    dst[4 * q] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
+  }
+}
+template <int N>
+__device__ __forceinline__ void qkp_store(float* dst, const float* src) {
+#pragma unroll
+  for (int q = 0; q < N / 4; ++q)
+    *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(src[4 * q], src[4 * q + 1], src[4 * q + 2], src[4 * q + 3]);
+}
 
 template <typename T, typename W>
 __global__ void __launch_bounds__(QKP_THREADS)
@@ -32,25 +48,23 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   KVB_KERNEL_PROLOGUE(KVB_TAG_QK_PREPARE);
   extern __shared__ float smem[];
   const int heads = H + KVH;
+  const int half = rot >> 1;
+  const bool turn = cos_sin != nullptr && half > 0;
+  const int q_len = norm_mode == 1 ? H * D : norm_mode == 2 ? D : 0;
+  const int k_len = norm_mode == 1 ? KVH * D : norm_mode == 2 ? D : 0;
+  // Everything the later passes need from global memory is asked for before the first barrier: the row,
+  // the norm weights, this token's cos/sin and its page; after it the passes run on shared memory alone.
   float* x = smem;                       // [heads * D] (+ one pad after every 32): q heads then k heads, 32-bit
-  float* head_sq = smem + QKP_AT((size_t)heads * D) + 1;   // [heads]
+  float* head_sq = smem + QKP_AT((size_t)heads * D) + 4;   // [heads]; what follows starts on a 16-byte boundary
+  float2* cs = reinterpret_cast<float2*>(smem + ((QKP_AT((size_t)heads * D) + 4 + heads + 3) & ~(size_t)3));   // [half]
+  W* wsm = reinterpret_cast<W*>(cs + ((half + 1) & ~1));    // [q_len + k_len], 16-byte aligned
   const int token = blockIdx.x;
   const int pos = positions[token];
   T* row = rows + (size_t)token * row_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = QKP_THREADS / 32;
-
   constexpr int VN = Vec16<T>::N;   // `vec`: rows, heads and cache rows start on 16-byte boundaries
-  if (vec) {
-    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
-      Vec16<T> v;
-      v.load(row + i);
-#pragma unroll
-      for (int j = 0; j < VN; ++j) x[QKP_AT(i + j)] = v.get(j);
-    }
-  } else {
-    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[QKP_AT(i)] = to_float(row[i]);
-  }
-  __syncthreads();
+  // the last pass takes whole vectors (and their rotation partners) when the turned half is made of whole vectors
+  const bool fused = vec && (!turn || half % VN == 0);
 
   size_t cache_base = 0;
   bool write = k_cache != nullptr;
@@ -63,19 +77,56 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
     cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
   }
   const size_t head_stride = (size_t)page_size * D;
-  if (write) {
-    const T* v = value_mode == 1 ? row + (size_t)H * D : row + (size_t)(H + KVH) * D;
+  if (vec) {
+    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+      Vec16<T> v;
+      v.load(row + i);
+      float f[VN];
+#pragma unroll
+      for (int j = 0; j < VN; ++j) f[j] = v.get(j);
+      qkp_store<VN>(x + QKP_AT(i), f);
+    }
+  } else {
+    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[QKP_AT(i)] = to_float(row[i]);
+  }
+  constexpr int WN = Vec16<W>::N;
+  if (fused && q_len % WN == 0 && k_len % WN == 0 && aligned16(q_weight) && aligned16(k_weight)) {
+    for (int i = threadIdx.x * WN; i < q_len + k_len; i += QKP_THREADS * WN) {
+      Vec16<W> w;
+      w.load(i < q_len ? q_weight + i : k_weight + (i - q_len));
+      w.store(wsm + i);
+    }
+  } else {
+    for (int i = threadIdx.x; i < q_len + k_len; i += QKP_THREADS) wsm[i] = i < q_len ? q_weight[i] : k_weight[i - q_len];
+  }
+  if (turn)
+    for (int j = threadIdx.x; j < half; j += QKP_THREADS) cs[j] = cos_sin[(size_t)token * half + j];
+  if (write && value_mode == 0) {      // values of their own: a copy that depends on nothing else here
+    const T* v = row + (size_t)(H + KVH) * D;
     if (vec) {
       for (int i = threadIdx.x * VN; i < KVH * D; i += QKP_THREADS * VN) {
-        const int vh = i / D, d = i % D;
         Vec16<T> t;
         t.load(v + i);
-        t.store(v_cache + cache_base + (size_t)vh * head_stride + d);
+        t.store(v_cache + cache_base + (size_t)(i / D) * head_stride + i % D);
       }
     } else {
-      for (int i = threadIdx.x; i < KVH * D; i += QKP_THREADS) {
-        const int vh = i / D, d = i % D;
-        v_cache[cache_base + (size_t)vh * head_stride + d] = v[i];
+      for (int i = threadIdx.x; i < KVH * D; i += QKP_THREADS)
+        v_cache[cache_base + (size_t)(i / D) * head_stride + i % D] = v[i];
+    }
+  }
+  __syncthreads();
+
+  if (write && value_mode == 1) {      // the values are the keys as projected: exact in 32-bit, stored back as they were
+    const int step = vec ? VN : 1;
+    for (int i = threadIdx.x * step; i < KVH * D; i += QKP_THREADS * step) {
+      T* dst = v_cache + cache_base + (size_t)(i / D) * head_stride + i % D;
+      if (vec) {
+        Vec16<T> t;
+#pragma unroll
+        for (int j = 0; j < VN; ++j) t.set(j, x[QKP_AT(H * D + i + j)]);
+        t.store(dst);
+      } else {
+        dst[0] = from_float<T>(x[QKP_AT(H * D + i)]);
       }
     }
   }
@@ -97,38 +148,64 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
       q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
       k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
     }
-    const int step = vec ? VN : 1;
-    for (int i = threadIdx.x * step; i < heads * D; i += QKP_THREADS * step) {
-      const int h = i / D, d = i % D;       // a vector never crosses a head: D is a multiple of its length
-      const float scale = norm_mode == 1 ? (h < H ? q_inv : k_inv) : 1.0f / sqrtf(head_sq[h] / (float)D + eps);
-      const W* w = norm_mode == 1 ? (h < H ? q_weight + i : k_weight + (i - H * D)) : (h < H ? q_weight + d : k_weight + d);
+    if (fused) {
+      // The vector pass below scales on the fly: value(i) = x[i] * scale(head) * w(i).
+      // A vector and its rotation partner lie in one head; `base + j` addresses element i + j (a vector of 8
+      // never crosses a pad).
+      for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+        const int h = i / D, d = i - h * D;
+        const float scale = norm_mode == 1 ? (h < H ? q_inv : k_inv) : 1.0f / sqrtf(head_sq[h] / (float)D + eps);
+        const int w_at = norm_mode == 1 ? i : (h < H ? d : q_len + d);
+        float own[VN];
+        qkp_load<VN>(own, x + QKP_AT(i));
 #pragma unroll
-      for (int j = 0; j < VN; ++j)
-        if (j < step) x[QKP_AT(i + j)] = x[QKP_AT(i + j)] * scale * to_float(w[j]);
+        for (int j = 0; j < VN; ++j) own[j] *= scale * to_float(wsm[w_at + j]);
+        Vec16<T> v;
+        if (turn && d < rot) {
+          const bool low = d < half;
+          const int mate = low ? half : -half;
+          float other[VN];
+          qkp_load<VN>(other, x + QKP_AT(i + mate));
+          const float2* t = cs + (low ? d : d - half);
+#pragma unroll
+          for (int j = 0; j < VN; ++j) {
+            const float o = other[j] * scale * to_float(wsm[w_at + mate + j]);
+            v.set(j, low ? own[j] * t[j].x - o * t[j].y : own[j] * t[j].x + o * t[j].y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < VN; ++j) v.set(j, own[j]);
+        }
+        v.store(row + i);
+        if (h >= H && write) v.store(k_cache + cache_base + (size_t)(h - H) * head_stride + d);
+      }
+      return;
     }
-    __syncthreads();
-  }
-
-  const int half = rot >> 1;
-  const bool turn = cos_sin != nullptr && half > 0;
-  __syncthreads();   // the values were copied from the row that is overwritten from here on
-  if (vec && (!turn || half % VN == 0)) {
-    // rotation and store in one pass: a vector of the turned part takes its partner vector from shared memory
-    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+    for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) {
       const int h = i / D, d = i % D;
+      const float scale = norm_mode == 1 ? (h < H ? q_inv : k_inv) : 1.0f / sqrtf(head_sq[h] / (float)D + eps);
+      const int at = norm_mode == 1 ? i : (h < H ? d : q_len + d);
+      x[QKP_AT(i)] = x[QKP_AT(i)] * scale * to_float(wsm[at]);
+    }
+  }
+  __syncthreads();   // (also: the values were copied from what is overwritten from here on)
+
+  if (fused) {
+    // no norm: rotation and store in one pass, a vector of the turned part taking its partner from shared memory
+    for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
+      const int h = i / D, d = i - h * D;
+      const int base = QKP_AT(i);
       Vec16<T> v;
       if (turn && d < rot) {
         const bool low = d < half;
-        const int mate = low ? i + half : i - half;
-        const float2* cs = cos_sin + (size_t)token * half + (low ? d : d - half);
+        const int mate_base = QKP_AT(low ? i + half : i - half);
+        const float2* t = cs + (low ? d : d - half);
 #pragma unroll
-        for (int j = 0; j < VN; ++j) {
-          const float2 t = cs[j];
-          v.set(j, low ? x[QKP_AT(i + j)] * t.x - x[QKP_AT(mate + j)] * t.y : x[QKP_AT(i + j)] * t.x + x[QKP_AT(mate + j)] * t.y);
-        }
+        for (int j = 0; j < VN; ++j)
+          v.set(j, low ? x[base + j] * t[j].x - x[mate_base + j] * t[j].y : x[base + j] * t[j].x + x[mate_base + j] * t[j].y);
       } else {
 #pragma unroll
-        for (int j = 0; j < VN; ++j) v.set(j, x[QKP_AT(i + j)]);
+        for (int j = 0; j < VN; ++j) v.set(j, x[base + j]);
       }
       v.store(row + i);
       if (h >= H && write) v.store(k_cache + cache_base + (size_t)(h - H) * head_stride + d);
@@ -138,11 +215,11 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   if (turn) {
     for (int item = threadIdx.x; item < heads * half; item += QKP_THREADS) {
       const int h = item / half, j = item % half;
-      const float2 cs = cos_sin[(size_t)token * half + j];
+      const float2 t = cs[j];
       const int lo = h * D + j, hi = lo + half;
       const float a = x[QKP_AT(lo)], b = x[QKP_AT(hi)];
-      x[QKP_AT(lo)] = a * cs.x - b * cs.y;
-      x[QKP_AT(hi)] = b * cs.x + a * cs.y;
+      x[QKP_AT(lo)] = a * t.x - b * t.y;
+      x[QKP_AT(hi)] = b * t.x + a * t.y;
     }
     __syncthreads();
   }
@@ -174,7 +251,9 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "qk_prepare: no status word");
   const size_t elems = (size_t)(H + KVH) * D;
-  const size_t smem = (QKP_AT(elems) + 1 + (size_t)(H + KVH)) * sizeof(float);
+  const size_t norm_len = norm_mode == 1 ? elems : norm_mode == 2 ? 2 * (size_t)D : 0;
+  const size_t smem = (QKP_AT(elems) + 8 + (size_t)(H + KVH)) * sizeof(float) + (size_t)(rot / 2 + 2) * sizeof(float2) +
+                      norm_len * sizeof(float);
   KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
   const int esize = dtype == KVB_F32 ? 4 : 2;
   const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&

@@ -30,6 +30,18 @@ __device__ __forceinline__ void qkp_load(float* dst, const float* src) {
     dst[4 * q] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
   }
 }
+// N norm weights from shared memory (16-byte aligned, N * sizeof(W) a multiple of 16 bytes) as 32-bit values
+template <typename W, int N>
+__device__ __forceinline__ void qkp_weights(float* dst, const W* src) {
+  constexpr int PER = 16 / sizeof(W);
+#pragma unroll
+  for (int q = 0; q < N / PER; ++q) {
+    Vec16<W> v;
+    v.load(src + q * PER);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) dst[q * PER + j] = v.get(j);
+  }
+}
 template <int N>
 __device__ __forceinline__ void qkp_store(float* dst, const float* src) {
 #pragma unroll
@@ -64,7 +76,7 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = QKP_THREADS / 32;
   constexpr int VN = Vec16<T>::N;   // `vec`: rows, heads and cache rows start on 16-byte boundaries
   // the last pass takes whole vectors (and their rotation partners) when the turned half is made of whole vectors
-  const bool fused = vec && (!turn || half % VN == 0);
+  const bool fused = vec && (!turn || half % VN == 0) && (VN * sizeof(W)) % 16 == 0;
 
   size_t cache_base = 0;
   bool write = k_cache != nullptr;
@@ -139,12 +151,15 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
       if (lane == 0) head_sq[h] = sq;
     }
     __syncthreads();
-    // every thread forms the scales itself, adding the heads' sums in ascending order
     float q_inv = 0.0f, k_inv = 0.0f;
     if (norm_mode == 1) {
+      // every warp adds the heads' sums the same way: lane l takes heads l, l + 32, ... in ascending order,
+      // then the butterfly
       float q_sq = 0.0f, k_sq = 0.0f;
-      for (int h = 0; h < H; ++h) q_sq += head_sq[h];
-      for (int h = H; h < heads; ++h) k_sq += head_sq[h];
+      for (int h = lane; h < H; h += 32) q_sq += head_sq[h];
+      for (int h = H + lane; h < heads; h += 32) k_sq += head_sq[h];
+      q_sq = warp_sum(q_sq);
+      k_sq = warp_sum(k_sq);
       q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
       k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
     }
@@ -156,21 +171,23 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
         const int h = i / D, d = i - h * D;
         const float scale = norm_mode == 1 ? (h < H ? q_inv : k_inv) : 1.0f / sqrtf(head_sq[h] / (float)D + eps);
         const int w_at = norm_mode == 1 ? i : (h < H ? d : q_len + d);
-        float own[VN];
+        float own[VN], wv[VN];
         qkp_load<VN>(own, x + QKP_AT(i));
+        qkp_weights<W, VN>(wv, wsm + w_at);
 #pragma unroll
-        for (int j = 0; j < VN; ++j) own[j] *= scale * to_float(wsm[w_at + j]);
+        for (int j = 0; j < VN; ++j) own[j] *= scale * wv[j];
         Vec16<T> v;
         if (turn && d < rot) {
           const bool low = d < half;
           const int mate = low ? half : -half;
-          float other[VN];
+          float other[VN], t[2 * VN];
           qkp_load<VN>(other, x + QKP_AT(i + mate));
-          const float2* t = cs + (low ? d : d - half);
+          qkp_weights<W, VN>(wv, wsm + w_at + mate);
+          qkp_load<2 * VN>(t, reinterpret_cast<const float*>(cs + (low ? d : d - half)));   // (cos, sin) pairs
 #pragma unroll
           for (int j = 0; j < VN; ++j) {
-            const float o = other[j] * scale * to_float(wsm[w_at + mate + j]);
-            v.set(j, low ? own[j] * t[j].x - o * t[j].y : own[j] * t[j].x + o * t[j].y);
+            const float o = other[j] * scale * wv[j];
+            v.set(j, low ? own[j] * t[2 * j] - o * t[2 * j + 1] : own[j] * t[2 * j] + o * t[2 * j + 1]);
           }
         } else {
 #pragma unroll
@@ -253,7 +270,7 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   const size_t elems = (size_t)(H + KVH) * D;
   const size_t norm_len = norm_mode == 1 ? elems : norm_mode == 2 ? 2 * (size_t)D : 0;
   const size_t smem = (QKP_AT(elems) + 8 + (size_t)(H + KVH)) * sizeof(float) + (size_t)(rot / 2 + 2) * sizeof(float2) +
-                      norm_len * sizeof(float);
+                      norm_len * (weight_dtype == KVB_F32 ? 4 : 2);
   KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
   const int esize = dtype == KVB_F32 ? 4 : 2;
   const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&

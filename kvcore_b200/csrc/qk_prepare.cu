@@ -70,6 +70,8 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   float* head_sq = smem + QKP_AT((size_t)heads * D) + 4;   // [heads]; what follows starts on a 16-byte boundary
   float2* cs = reinterpret_cast<float2*>(smem + ((QKP_AT((size_t)heads * D) + 4 + heads + 3) & ~(size_t)3));   // [half]
   W* wsm = reinterpret_cast<W*>(cs + ((half + 1) & ~1));    // [q_len + k_len], 16-byte aligned
+  // [heads * D / VN] sums of squares, one per vector of the load pass (vector path with a norm only)
+  float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(wsm) + (((size_t)(q_len + k_len) * sizeof(W) + 15) & ~(size_t)15));
   const int token = blockIdx.x;
   const int pos = positions[token];
   T* row = rows + (size_t)token * row_stride;
@@ -93,10 +95,11 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
     for (int i = threadIdx.x * VN; i < heads * D; i += QKP_THREADS * VN) {
       Vec16<T> v;
       v.load(row + i);
-      float f[VN];
+      float f[VN], sq = 0.0f;
 #pragma unroll
-      for (int j = 0; j < VN; ++j) f[j] = v.get(j);
+      for (int j = 0; j < VN; ++j) { f[j] = v.get(j); sq = fmaf(f[j], f[j], sq); }
       qkp_store<VN>(x + QKP_AT(i), f);
+      if (norm_mode != 0) part[i / VN] = sq;
     }
   } else {
     for (int i = threadIdx.x; i < heads * D; i += QKP_THREADS) x[QKP_AT(i)] = to_float(row[i]);
@@ -146,7 +149,12 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   if (norm_mode != 0) {
     for (int h = warp; h < heads; h += nwarps) {
       float sq = 0.0f;
-      for (int d = lane; d < D; d += 32) { const float v = x[QKP_AT(h * D + d)]; sq = fmaf(v, v, sq); }
+      if (vec) {     // the vectors' sums of the load pass, lane-strided over the head's vectors
+        const int per_head = D / VN;
+        for (int v = lane; v < per_head; v += 32) sq += part[h * per_head + v];
+      } else {
+        for (int d = lane; d < D; d += 32) { const float v = x[QKP_AT(h * D + d)]; sq = fmaf(v, v, sq); }
+      }
       sq = warp_sum(sq);
       if (lane == 0) head_sq[h] = sq;
     }
@@ -270,7 +278,7 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   const size_t elems = (size_t)(H + KVH) * D;
   const size_t norm_len = norm_mode == 1 ? elems : norm_mode == 2 ? 2 * (size_t)D : 0;
   const size_t smem = (QKP_AT(elems) + 8 + (size_t)(H + KVH)) * sizeof(float) + (size_t)(rot / 2 + 2) * sizeof(float2) +
-                      norm_len * (weight_dtype == KVB_F32 ? 4 : 2);
+                      norm_len * (weight_dtype == KVB_F32 ? 4 : 2) + 16 + (norm_mode != 0 ? elems / 4 + 1 : 0) * sizeof(float);
   KVB_REQUIRE(smem <= 200 * 1024, "qk_prepare: the projections of one token do not fit in shared memory");
   const int esize = dtype == KVB_F32 ? 4 : 2;
   const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&

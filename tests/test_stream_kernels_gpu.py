@@ -57,6 +57,9 @@ QK_CASES = [
     (5, 1, 80, 0, None, True, 4),
     (8, 2, 64, 32, None, False, 16),
     (2, 2, 32, 2, "projection", False, 16),
+    (3, 1, 20, 10, "projection", True, 4),      # no 16-byte vector fits the head
+    (4, 2, 24, 12, "head", True, 8),            # vectors fit the head but not the turned half
+    (40, 8, 128, 128, "projection", True, 16),  # the whole head turned, several vectors a thread
 ]
 
 

@@ -55,6 +55,9 @@ CONFIGS = {
         attn(heads=3, kv_heads=3, dim=32, window=20, keep_first=0, rot_dims=32, scale=0.3, mlp=None),
         attn(heads=3, kv_heads=3, dim=32, window=5, keep_first=7, rot_dims=2, base=50.0, mlp=T.moe_mlp(3, 1, 24)),
         attn(heads=2, kv_heads=1, dim=48, window=33, keep_first=1, rot_dims=0 + 16, mlp=T.moe_mlp(4, 4, 8, shared_ff=8)),
+        # a head size and a turned part that no 16-byte vector fits, more kept positions than the window is long
+        attn(heads=2, kv_heads=2, dim=20, window=9, keep_first=12, rot_dims=10, mlp=T.dense_mlp(24, limit=2.0)),
+        attn(heads=4, kv_heads=1, dim=24, window=70, keep_first=3, rot_dims=12, mlp=T.moe_mlp(1, 1, 16)),
     ], vocab=61, width=40, eps=1e-6),
     # head sizes of the serving kernels (tensor-core prompt and decode kernels on the GPU), windows of
     # several pages, kept positions that end inside a page

@@ -412,11 +412,16 @@ extern "C" int kvb_moe_gemv(void* out, const void* a, long long a_stride, int a_
   return 0;
 }
 
-// The same for a few hundred pairs: the pairs of one expert share one pass over its matrices.  grid (N / 32,
+// The same for a few hundred pairs: the pairs of one expert share one pass over its matrices.  grid (N / 128,
 // 2 * tiles): a block takes one half (8 rows) of a tile of the grouped order (moe_align), holds those pairs'
-// input rows in shared memory and gives each warp 4 output columns (GATED: 4 gate and 4 up rows) for all
-// 8 rows; a weight vector is loaded once and used for every row.
+// input rows in shared memory and gives each warp 2 output columns (GATED: 2 gate and 2 up rows) for all
+// 8 rows, 8 such groups of 16 columns one after the other; a weight vector is loaded once and used for every
+// row, the staged rows for 128 columns.  (Four columns a warp cost 176 registers and left one block a
+// multiprocessor; one group of columns a block spent more bytes on staging the rows than on weights.)
 #define MOE_GEMV_ROWS 8
+#define MOE_GEMV_ROWS_CPW 2                                  // output columns a warp (GATED: that many gate and up rows)
+#define MOE_GEMV_ROWS_COLS (8 * MOE_GEMV_ROWS_CPW)           // output columns of one group: 8 warps
+#define MOE_GEMV_ROWS_GROUPS 8                               // groups of columns a block walks with the rows it staged
 template <bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemv_rows_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, long long a_stride, int a_row_div,
@@ -451,15 +456,19 @@ moe_gemv_rows_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, long lo
     v.store(xs + i);
   }
   __syncthreads();
+  constexpr int CPW = MOE_GEMV_ROWS_CPW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * MOE_GEMV_COLS + warp * 4;
   const bf16* we = w + (size_t)expert * (GATED ? 2 : 1) * N * K;
-  constexpr int COLS = GATED ? 8 : 4;
+  constexpr int COLS = GATED ? 2 * CPW : CPW;
+  // the staged rows serve MOE_GEMV_ROWS_GROUPS groups of columns, one after the other
+  for (int group = 0; group < MOE_GEMV_ROWS_GROUPS; ++group) {
+  const int n0 = (blockIdx.x * MOE_GEMV_ROWS_GROUPS + group) * MOE_GEMV_ROWS_COLS + warp * CPW;
+  if (n0 >= N) break;                                        // uniform over the warp
   const bf16* cols[COLS];
   float acc[COLS][MOE_GEMV_ROWS];
 #pragma unroll
   for (int c = 0; c < COLS; ++c) {
-    const int n = min(n0 + (c & 3), N - 1) + (c >= 4 ? N : 0);
+    const int n = min(n0 + (c % CPW), N - 1) + (c >= CPW ? N : 0);
     cols[c] = we + (size_t)n * K;
 #pragma unroll
     for (int r = 0; r < MOE_GEMV_ROWS; ++r) acc[c][r] = 0.0f;
@@ -484,24 +493,25 @@ moe_gemv_rows_kernel(bf16* __restrict__ out, const bf16* __restrict__ a, long lo
   for (int c = 0; c < COLS; ++c)
 #pragma unroll
     for (int r = 0; r < MOE_GEMV_ROWS; ++r) acc[c][r] = warp_sum(acc[c][r]);
-  // lane (r, c) = (lane / 4, lane % 4) writes one output
-  const int r = lane >> 2, c = lane & 3;
+  // lane (r, c) = (lane / CPW, lane % CPW) of the first 8 * CPW lanes writes one output
+  const int r = lane / CPW, c = lane % CPW;
   float v = 0.0f, u = 0.0f;
 #pragma unroll
   for (int rr = 0; rr < MOE_GEMV_ROWS; ++rr)
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc)
+    for (int cc = 0; cc < CPW; ++cc)
       if (rr == r && cc == c) {
         v = acc[cc][rr];
-        if (GATED) u = acc[(cc + 4) % COLS][rr];
+        if (GATED) u = acc[(cc + CPW) % COLS][rr];
       }
-  const int pair = pair_of[r];
+  const int pair = lane < MOE_GEMV_ROWS * CPW ? pair_of[r] : -1;
   if (pair >= 0 && n0 + c < N) {
     if (GATED) {
       const float g = to_float(from_float<bf16>(v));
       v = to_float(from_float<bf16>(moe_silu<bf16>(g))) * to_float(from_float<bf16>(u));
     }
     out[(size_t)pair * N + n0 + c] = from_float<bf16>(v);
+  }
   }
 }
 
@@ -514,7 +524,8 @@ extern "C" int kvb_moe_gemv_rows(void* out, const void* a, long long a_stride, i
   KVB_REQUIRE(2 * (long long)max_tiles <= 65535, "moe_gemv_rows: too many tiles for one launch");
   const size_t smem = (size_t)MOE_GEMV_ROWS * K * sizeof(bf16);
   KVB_REQUIRE(smem <= 200 * 1024, "moe_gemv_rows: the input rows do not fit in shared memory");
-  dim3 grid((N + MOE_GEMV_COLS - 1) / MOE_GEMV_COLS, 2 * max_tiles);
+  const int block_cols = MOE_GEMV_ROWS_COLS * MOE_GEMV_ROWS_GROUPS;
+  dim3 grid((N + block_cols - 1) / block_cols, 2 * max_tiles);
 #define KVB_MOE_GEMV_ROWS(G_)                                                                                 \
   do {                                                                                                        \
     if (smem > 48 * 1024)                                                                                     \

@@ -316,3 +316,46 @@ def test_greedy_generation_through_the_entry_point(device, tmp_path, name, budge
     kv = engine.engine_core.model_runner.kv_manager
     kv.check_invariants()
     assert not kv.live_requests()
+
+
+# ---- the programs, each in a process of its own ------------------------------------------------------------
+@pytest.mark.gpu
+def test_offline_batch_program_on_a_toposun_folder(tmp_path):
+    import ast
+    import re
+    import subprocess
+    import sys
+
+    cfg = CONFIGS["serving_heads"]
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=4)
+    prompts = {f"req-{i}": rc.random_tokens(cfg["vocab"], n, 80 + i) for i, n in enumerate((70, 9, 33))}
+    (tmp_path / "requests.json").write_text(json.dumps(
+        [dict(request_id=rid, prompt_token_ids=tokens) for rid, tokens in prompts.items()]))
+    command = [sys.executable, str(rc.ROOT / "bin" / "kvcore_offline_batch"), "--model", str(folder), "--dtype", "float32",
+               "--prompt-tokens-file", str(tmp_path / "requests.json"), "--max-tokens", "6", "--block-size", "16",
+               "--num-gpu-blocks", "64", "--max-model-len", "256", "--max-num-seqs", "4",
+               "--max-num-scheduled-tokens", "48", "--max-num-partial-prefills", "4", "--max-long-partial-prefills", "4",
+               "--log-level", "WARNING"]
+    result = subprocess.run(command, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr[-2000:]
+    found = {m["id"]: list(ast.literal_eval(m["ids"])) for m in re.finditer(
+        r"^\[(?P<id>[^\]]+)\] finish_reason=\S+\ntoken_ids=(?P<ids>\(.*\))$", result.stdout, re.M)}
+    assert list(found) == list(prompts)
+    for rid, prompt in prompts.items():
+        assert found[rid] == plain_greedy(cfg, weights, prompt, 6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program_on_a_toposun_folder(case, dtype, tmp_path):
+    """``bin/trace_run`` as a user drives it: a step, its ``done`` line, the next step."""
+    if case["name"] != "serving_heads":
+        pytest.skip("one configuration is enough for the subprocess run")
+    steps = rc.trace_mixed(case["requests"], max_live=3, seed=5)
+    steps.insert(1, {"step": 1000, "entries": [], "end": []})      # a step that brings nothing
+    out = tmp_path / "out"
+    rc.run_subprocess(case["folder"], dtype, steps, out, rc.peak_tokens(steps))
+    rows = rc.collect(steps, out, case["cfg"]["vocab"])
+    assert len(rows) == sum(len(t) for t in case["requests"].values())
+    compare(rows, case["reference"], dtype, case["close_calls"])

@@ -157,6 +157,23 @@ def test_moe_experts_and_combine(dtype, tokens, experts, top, width, ff, on_inpu
         torch.testing.assert_close(got.rows, want, **t)
 
 
+@pytest.mark.parametrize("path", ["library", "stream", "tiles"])
+def test_moe_experts_when_one_expert_takes_nearly_all(path):
+    """Nearly every pair on one of 64 experts (the batched products at a common stride would be mostly padding,
+    so the library path goes expert by expert), a few experts with one pair, most with none."""
+    tokens, experts, top, width, ff = 200, 64, 1, 64, 32
+    x = randn(tokens, width, dtype=torch.bfloat16, seed=1)
+    gate_up = randn(experts, 2 * ff, width, dtype=torch.bfloat16, seed=2, scale=0.2)
+    down = randn(experts, width, ff, dtype=torch.bfloat16, seed=3, scale=0.2)
+    ids = torch.full((tokens, top), 5, dtype=torch.int32, device=DEV)
+    ids[::37, 0] = torch.arange(0, tokens, 37, dtype=torch.int32, device=DEV) % experts
+    weights = torch.rand(tokens, top, device=DEV) + 0.5
+    want = P.moe_combine(P.moe_experts(x, ids, weights, gate_up, down, weight_on_input=True), tokens, top)
+    got = K().moe_combine(K().moe_experts(x, ids, weights, gate_up, down, weight_on_input=True, path=path), tokens, top)
+    assert K().read_status() == 0
+    torch.testing.assert_close(got, want, rtol=3e-2, atol=0.02 * float(want.float().abs().max()))
+
+
 def test_moe_rows_do_not_depend_on_the_batch():
     tokens, experts, top, width, ff = 50, 6, 2, 128, 48
     x = randn(tokens, width, dtype=torch.float32, seed=1)

@@ -258,6 +258,151 @@ qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const int* __restr
   }
 }
 
+// The same work for rows that are made of whole 16-byte vectors and few enough of them that a thread can keep
+// its own (at most QKP_REG_VECTORS) in registers from the load to the store: the row, the norm weights of a
+// thread's vectors and of their rotation partners are asked for at once; shared memory only carries the raw row
+// (for the partners of the rotation and the values), the vectors' sums of squares and this token's cos/sin.
+#define QKP_REG_VECTORS 3
+template <typename T, typename W>
+__global__ void __launch_bounds__(QKP_THREADS, 4)
+qk_prepare_regs_kernel(T* __restrict__ rows, long long row_stride, const int* __restrict__ positions,
+                       const int* __restrict__ req_index, const float2* __restrict__ cos_sin,
+                       const W* __restrict__ q_weight, const W* __restrict__ k_weight,
+                       const int* __restrict__ table, int table_stride, T* __restrict__ k_cache,
+                       T* __restrict__ v_cache, int H, int KVH, int D, int rot, int norm_mode, int value_mode,
+                       float eps, int page_size, int num_pages, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_QK_PREPARE);
+  extern __shared__ __align__(16) unsigned char regs_smem[];
+  constexpr int VN = Vec16<T>::N;
+  const int heads = H + KVH, total = heads * D, nvec = total / VN;
+  const int half = rot >> 1;
+  const bool turn = cos_sin != nullptr && half > 0;
+  const int q_len = norm_mode == 1 ? H * D : D;
+  T* raw = reinterpret_cast<T*>(regs_smem);                                   // [total]
+  float* part = reinterpret_cast<float*>(raw + total);                        // [nvec]
+  float* head_sq = part + ((nvec + 3) & ~3);                                  // [max(heads, 2 * warps)]
+  float2* cs = reinterpret_cast<float2*>(head_sq + ((max(heads, 2 * (QKP_THREADS / 32)) + 3) & ~3));   // [half]
+  const int token = blockIdx.x;
+  const int pos = positions[token];
+  T* row = rows + (size_t)token * row_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = QKP_THREADS / 32;
+
+  size_t cache_base = 0;
+  bool write = k_cache != nullptr;
+  if (write) {
+    const int page = table[(size_t)req_index[token] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      write = false;
+    }
+    cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
+  }
+  const size_t head_stride = (size_t)page_size * D;
+
+  Vec16<T> mine[QKP_REG_VECTORS];
+  Vec16<W> w_own[QKP_REG_VECTORS], w_mate[QKP_REG_VECTORS];
+#pragma unroll
+  for (int n = 0; n < QKP_REG_VECTORS; ++n) {
+    const int i = (threadIdx.x + n * QKP_THREADS) * VN;
+    if (i < total) {
+      mine[n].load(row + i);
+      if (norm_mode != 0) {
+        const int h = i / D, d = i - h * D;
+        const int at = norm_mode == 1 ? i : (h < H ? d : q_len + d);
+        w_own[n].load(at < q_len ? q_weight + at : k_weight + (at - q_len));
+        if (turn && d < rot) {
+          const int mate = at + (d < half ? half : -half);
+          w_mate[n].load(mate < q_len ? q_weight + mate : k_weight + (mate - q_len));
+        }
+      }
+    }
+  }
+  if (turn)
+    for (int j = threadIdx.x; j < half; j += QKP_THREADS) cs[j] = cos_sin[(size_t)token * half + j];
+  if (write && value_mode == 0) {
+    const T* v = row + (size_t)(H + KVH) * D;
+    for (int i = threadIdx.x * VN; i < KVH * D; i += QKP_THREADS * VN) {
+      Vec16<T> t;
+      t.load(v + i);
+      t.store(v_cache + cache_base + (size_t)(i / D) * head_stride + i % D);
+    }
+  }
+  float my_q = 0.0f, my_k = 0.0f;      // this thread's share of the two sums of squares (its vectors in order)
+#pragma unroll
+  for (int n = 0; n < QKP_REG_VECTORS; ++n) {
+    const int i = (threadIdx.x + n * QKP_THREADS) * VN;
+    if (i < total) {
+      mine[n].store(raw + i);
+      float sq = 0.0f;
+#pragma unroll
+      for (int j = 0; j < VN; ++j) { const float f = mine[n].get(j); sq = fmaf(f, f, sq); }
+      if (norm_mode == 2) part[i / VN] = sq;
+      if (i < H * D) my_q += sq; else my_k += sq;
+    }
+  }
+  if (norm_mode == 1) {                // one barrier: a butterfly per warp, then the warps' sums in ascending order
+    my_q = warp_sum(my_q);
+    my_k = warp_sum(my_k);
+    if (lane == 0) { head_sq[warp] = my_q; head_sq[nwarps + warp] = my_k; }
+  }
+  __syncthreads();
+
+  if (write && value_mode == 1) {      // the values are the keys as projected
+    for (int i = threadIdx.x * VN; i < KVH * D; i += QKP_THREADS * VN) {
+      Vec16<T> t;
+      t.load(raw + H * D + i);
+      t.store(v_cache + cache_base + (size_t)(i / D) * head_stride + i % D);
+    }
+  }
+  float q_inv = 1.0f, k_inv = 1.0f;
+  if (norm_mode == 1) {
+    float q_sq = 0.0f, k_sq = 0.0f;
+#pragma unroll
+    for (int wi = 0; wi < QKP_THREADS / 32; ++wi) { q_sq += head_sq[wi]; k_sq += head_sq[QKP_THREADS / 32 + wi]; }
+    q_inv = 1.0f / sqrtf(q_sq / (float)(H * D) + eps);
+    k_inv = KVH > 0 ? 1.0f / sqrtf(k_sq / (float)(KVH * D) + eps) : 0.0f;
+  } else if (norm_mode == 2) {
+    const int per_head = D / VN;
+    for (int h = warp; h < heads; h += nwarps) {
+      float sq = 0.0f;
+      for (int v = lane; v < per_head; v += 32) sq += part[h * per_head + v];
+      sq = warp_sum(sq);
+      if (lane == 0) head_sq[h] = sq;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int n = 0; n < QKP_REG_VECTORS; ++n) {
+    const int i = (threadIdx.x + n * QKP_THREADS) * VN;
+    if (i >= total) continue;
+    const int h = i / D, d = i - h * D;
+    float scale = 1.0f;
+    if (norm_mode == 1) scale = h < H ? q_inv : k_inv;
+    else if (norm_mode == 2) scale = 1.0f / sqrtf(head_sq[h] / (float)D + eps);
+    float own[VN];
+#pragma unroll
+    for (int j = 0; j < VN; ++j) own[j] = norm_mode != 0 ? mine[n].get(j) * scale * w_own[n].get(j) : mine[n].get(j);
+    Vec16<T> v;
+    if (turn && d < rot) {
+      const bool low = d < half;
+      Vec16<T> m;
+      m.load(raw + i + (low ? half : -half));
+      float t[2 * VN];
+      qkp_load<2 * VN>(t, reinterpret_cast<const float*>(cs + (low ? d : d - half)));
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        const float o = norm_mode != 0 ? m.get(j) * scale * w_mate[n].get(j) : m.get(j);
+        v.set(j, low ? own[j] * t[2 * j] - o * t[2 * j + 1] : own[j] * t[2 * j] + o * t[2 * j + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VN; ++j) v.set(j, own[j]);
+    }
+    v.store(row + i);
+    if (h >= H && write) v.store(k_cache + cache_base + (size_t)(h - H) * head_stride + d);
+  }
+}
+
 extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* positions, const int* req_index,
                               const float* cos_sin, const void* q_weight, const void* k_weight, const int* table,
                               int table_stride, void* k_cache, void* v_cache, int tokens, int H, int KVH, int D,
@@ -283,6 +428,28 @@ extern "C" int kvb_qk_prepare(void* rows, long long row_stride, const int* posit
   const int esize = dtype == KVB_F32 ? 4 : 2;
   const int vec = ((size_t)D * esize) % 16 == 0 && ((size_t)row_stride * esize) % 16 == 0 && aligned16(rows) &&
                   (k_cache == nullptr || (aligned16(k_cache) && aligned16(v_cache)));
+  const int vn = 16 / esize;
+  const bool weights_ok = norm_mode == 0 || (dtype == weight_dtype && aligned16(q_weight) && (KVH == 0 || aligned16(k_weight)));
+  const bool in_registers = vec && weights_ok && (rot == 0 || cos_sin == nullptr || (rot / 2) % vn == 0) &&
+                            elems <= (size_t)QKP_THREADS * QKP_REG_VECTORS * vn;
+  const size_t nvec = elems / vn;
+  const size_t regs_smem = elems * esize + (((nvec + 3) & ~(size_t)3) + (((size_t)(H + KVH) + 2 * (QKP_THREADS / 32) + 3) & ~(size_t)3)) * sizeof(float) +
+                           (size_t)(rot / 2 + 2) * sizeof(float2);
+#define KVB_QKP_REGS(T_, W_)                                                                                \
+  do {                                                                                                      \
+    if (regs_smem > 48 * 1024)                                                                              \
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(qk_prepare_regs_kernel<T_, W_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)regs_smem)); \
+    KVB_CHECK_CUDA(kvb_launch((qk_prepare_regs_kernel<T_, W_>), dim3(tokens), dim3(QKP_THREADS), regs_smem, stream, true, \
+                              (T_*)rows, row_stride, positions, req_index, (const float2*)cos_sin,          \
+                              (const W_*)q_weight, (const W_*)k_weight, table, table_stride, (T_*)k_cache,  \
+                              (T_*)v_cache, H, KVH, D, rot, norm_mode, value_mode, eps, page_size, num_pages, status)); \
+  } while (0)
+  if (in_registers) {
+    if (dtype == KVB_F32) KVB_QKP_REGS(float, float); else KVB_QKP_REGS(bf16, bf16);
+    KVB_CHECK_LAUNCH();
+    return 0;
+  }
+#undef KVB_QKP_REGS
 #define KVB_QKP(T_, W_)                                                                                     \
   do {                                                                                                      \
     if (smem > 48 * 1024)                                                                                   \

@@ -86,6 +86,9 @@ def _register_stock_architectures() -> None:
     from .toposun import ARCHITECTURE, ToposunConfig
 
     register_architecture(ARCHITECTURE, lambda raw: ToposunConfig.from_dict(raw).to_model_spec())
+    from .pipesun import ARCHITECTURE as PIPESUN, PipesunConfig
+
+    register_architecture(PIPESUN, lambda raw: PipesunConfig.from_dict(raw).to_model_spec())
 
 
 _register_stock_architectures()

@@ -152,6 +152,15 @@ struct KvbTrace {
 #define KVB_TAG_MOE_COMBINE 24
 #define KVB_TAG_KEPT_FIRST 25
 #define KVB_TAG_MOE_GATHER 26
+#define KVB_TAG_RMS_SHIFT 27
+#define KVB_TAG_ADD_NORM 28
+#define KVB_TAG_ATTN_DIMS 29
+#define KVB_TAG_LATENT_PREPARE 30
+#define KVB_TAG_HEAD_NORM_KV 31
+#define KVB_TAG_MAPS_COMBINE 32
+#define KVB_TAG_GATE_MUL 33
+#define KVB_TAG_FLASH_DIMS 34
+#define KVB_TAG_FLASH_DIMS_COMBINE 35
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

@@ -1,0 +1,255 @@
+// Small kernels between the projections and the attention of two mixers, 32-bit inside, one rounding at
+// the store.
+//
+//   latent_prepare (latent attention: one cached vector a token).  A projected row holds `rank` latent
+//   entries and `rot` position entries.  The latent entries get an RMS norm with a weight; the position
+//   entries are turned by the token's position, entry 2i with entry 2i+1 (interleaved pairs), angle
+//   position * inv_freq[i], for the first `dims` of them.  Both go into the token's cached row
+//   [rank | rot].  The query rows [heads, width + rot] get the same turn on their last `rot` entries,
+//   written behind the `rank` entries of the attention's query rows [heads, rank + rot]; the first
+//   `rank` entries of those rows (the query carried into the latent space) are copied from `q_latent`
+//   when given, else left as the caller filled them.
+//
+//   head_norm_kv_write (attention with several score maps a head).  q and k are cut into vectors of
+//   `dim` entries (one per head and map); each gets an RMS norm of its own with one weight shared by
+//   all; q is normed in place, the normed k and the values go side by side into the token's cached row
+//   [k | v].
+//
+//   maps_combine: o = a1 - lambda * a2 of the two maps of a head (32-bit in), divided by its root mean
+//   square over the head's values, times a constant; written in the activation type.
+//
+//   sigmoid_gate_mul: out[t, h, :] = o[t, h, :] * sigmoid(g[t, h, :]), o with strides of its own.
+#include "common.cuh"
+
+#define MP_THREADS 128
+
+template <typename T>
+__global__ void __launch_bounds__(MP_THREADS)
+latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const T* __restrict__ norm_weight,
+                      float eps, const float* __restrict__ inv_freq, int dims, const int* __restrict__ positions,
+                      const int* __restrict__ req_index, const int* __restrict__ table, int table_stride,
+                      T* __restrict__ cache, int page_size, int num_pages, int write, const T* __restrict__ q,
+                      long long q_token_stride, long long q_head_stride, int q_width,
+                      const T* __restrict__ q_latent, long long ql_token_stride, long long ql_head_stride,
+                      T* __restrict__ q_out, int heads, int rank, int rot, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_LATENT_PREPARE);
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const float fpos = (float)pos;
+  const int row_width = rank + rot;
+  if (write) {
+    const T* src = kv_rows + (size_t)t * kv_stride;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < rank; i += MP_THREADS) {
+      const float v = to_float(src[i]);
+      ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
+    const int page = table[(size_t)req_index[t] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+    } else {
+      T* dst = cache + ((size_t)page * page_size + pos % page_size) * row_width;
+      for (int i = threadIdx.x; i < rank; i += MP_THREADS)
+        dst[i] = from_float<T>(to_float(src[i]) * inv * to_float(norm_weight[i]));
+      for (int i = threadIdx.x; i < rot / 2; i += MP_THREADS) {
+        float u = to_float(src[rank + 2 * i]), v = to_float(src[rank + 2 * i + 1]);
+        if (2 * i < dims) {
+          float s, c;
+          sincosf(fpos * inv_freq[i], &s, &c);
+          const float nu = u * c - v * s, nv = v * c + u * s;
+          u = nu; v = nv;
+        }
+        dst[rank + 2 * i] = from_float<T>(u);
+        dst[rank + 2 * i + 1] = from_float<T>(v);
+      }
+      if ((rot & 1) && threadIdx.x == 0) dst[rank + rot - 1] = src[rank + rot - 1];
+    }
+  }
+  // query rows: the turned position part behind the latent part
+  for (int i = threadIdx.x; i < heads * (rot / 2); i += MP_THREADS) {
+    const int h = i / (rot / 2), j = i % (rot / 2);
+    const T* src = q + (size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width;
+    float u = to_float(src[2 * j]), v = to_float(src[2 * j + 1]);
+    if (2 * j < dims) {
+      float s, c;
+      sincosf(fpos * inv_freq[j], &s, &c);
+      const float nu = u * c - v * s, nv = v * c + u * s;
+      u = nu; v = nv;
+    }
+    T* dst = q_out + ((size_t)t * heads + h) * row_width + rank;
+    dst[2 * j] = from_float<T>(u);
+    dst[2 * j + 1] = from_float<T>(v);
+  }
+  if (rot & 1)
+    for (int h = threadIdx.x; h < heads; h += MP_THREADS)
+      q_out[((size_t)t * heads + h) * row_width + rank + rot - 1] =
+          q[(size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + rot - 1];
+  if (q_latent != nullptr)
+    for (int i = threadIdx.x; i < heads * rank; i += MP_THREADS) {
+      const int h = i / rank, j = i % rank;
+      q_out[((size_t)t * heads + h) * row_width + j] =
+          q_latent[(size_t)t * ql_token_stride + (size_t)h * ql_head_stride + j];
+    }
+}
+
+extern "C" int kvb_latent_prepare(const void* kv_rows, long long kv_stride, const void* norm_weight, float eps,
+                                  const float* inv_freq, int dims, const int* positions, const int* req_index,
+                                  const int* table, int table_stride, void* cache, int page_size, int num_pages,
+                                  int write, const void* q, long long q_token_stride, long long q_head_stride,
+                                  int q_width, const void* q_latent, long long ql_token_stride,
+                                  long long ql_head_stride, void* q_out, int tokens, int heads, int rank, int rot,
+                                  int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  KVB_REQUIRE(rank > 0 && rot >= 0 && heads > 0 && dims >= 0 && dims <= rot && dims % 2 == 0,
+              "latent_prepare: bad sizes");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "latent_prepare: no status word");
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<float>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+        (const float*)kv_rows, kv_stride, (const float*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
+        table_stride, (float*)cache, page_size, num_pages, write, (const float*)q, q_token_stride, q_head_stride,
+        q_width, (const float*)q_latent, ql_token_stride, ql_head_stride, (float*)q_out, heads, rank, rot, status));
+  else
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<bf16>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+        (const bf16*)kv_rows, kv_stride, (const bf16*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
+        table_stride, (bf16*)cache, page_size, num_pages, write, (const bf16*)q, q_token_stride, q_head_stride,
+        q_width, (const bf16*)q_latent, ql_token_stride, ql_head_stride, (bf16*)q_out, heads, rank, rot, status));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MP_THREADS)
+head_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const T* __restrict__ q_weight,
+                          const T* __restrict__ k_weight, float eps, const int* __restrict__ positions,
+                          const int* __restrict__ req_index, const int* __restrict__ table, int table_stride,
+                          T* __restrict__ cache, int page_size, int num_pages, int write, int q_vectors,
+                          int k_vectors, int dim, int v_width, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_HEAD_NORM_KV);
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  T* row = rows + (size_t)t * row_stride;
+  T* dst = nullptr;
+  if (write) {
+    const int pos = positions[t];
+    const int page = table[(size_t)req_index[t] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+    } else {
+      dst = cache + ((size_t)page * page_size + pos % page_size) * ((size_t)k_vectors * dim + v_width);
+    }
+  }
+  const int vectors = q_vectors + (write ? k_vectors : 0);
+  for (int n = warp; n < vectors; n += MP_THREADS / 32) {
+    const bool is_q = n < q_vectors;
+    T* vec = row + (size_t)n * dim;
+    const T* w = is_q ? q_weight : k_weight;
+    float ss = 0.0f;
+    for (int i = lane; i < dim; i += 32) {
+      const float v = to_float(vec[i]);
+      ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+    T* o = is_q ? vec : (dst == nullptr ? nullptr : dst + (size_t)(n - q_vectors) * dim);
+    if (o != nullptr)
+      for (int i = lane; i < dim; i += 32) o[i] = from_float<T>(to_float(vec[i]) * inv * to_float(w[i]));
+  }
+  if (dst != nullptr) {
+    const T* v = row + (size_t)(q_vectors + k_vectors) * dim;
+    for (int i = threadIdx.x; i < v_width; i += MP_THREADS) dst[(size_t)k_vectors * dim + i] = v[i];
+  }
+}
+
+extern "C" int kvb_head_norm_kv_write(void* rows, long long row_stride, const void* q_weight, const void* k_weight,
+                                      float eps, const int* positions, const int* req_index, const int* table,
+                                      int table_stride, void* cache, int page_size, int num_pages, int write,
+                                      int tokens, int q_vectors, int k_vectors, int dim, int v_width, int dtype,
+                                      cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  KVB_REQUIRE(q_vectors > 0 && k_vectors > 0 && dim > 0 && v_width > 0, "head_norm_kv_write: bad sizes");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "head_norm_kv_write: no status word");
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<float>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+        (float*)rows, row_stride, (const float*)q_weight, (const float*)k_weight, eps, positions, req_index, table,
+        table_stride, (float*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
+  else
+    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<bf16>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+        (bf16*)rows, row_stride, (const bf16*)q_weight, (const bf16*)k_weight, eps, positions, req_index, table,
+        table_stride, (bf16*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MP_THREADS)
+maps_combine_kernel(T* __restrict__ out, const float* __restrict__ a, long long rows, int width, float lambda,
+                    float eps, float out_scale) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_MAPS_COMBINE);
+  const long long row = (long long)blockIdx.x * (MP_THREADS / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float* a1 = a + (size_t)row * 2 * width;
+  const float* a2 = a1 + width;
+  float ss = 0.0f;
+  for (int i = lane; i < width; i += 32) {
+    const float o = a1[i] - lambda * a2[i];
+    ss = fmaf(o, o, ss);
+  }
+  const float mul = out_scale / sqrtf(warp_sum(ss) / (float)width + eps);
+  for (int i = lane; i < width; i += 32) out[(size_t)row * width + i] = from_float<T>((a1[i] - lambda * a2[i]) * mul);
+}
+
+extern "C" int kvb_maps_combine(void* out, const float* a, long long rows, int width, float lambda, float eps,
+                                float out_scale, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  KVB_REQUIRE(width > 0, "maps_combine: width must be positive");
+  const long long blocks = (rows + MP_THREADS / 32 - 1) / (MP_THREADS / 32);
+  KVB_REQUIRE(blocks < (1ll << 31), "maps_combine: too many rows");
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((maps_combine_kernel<float>), dim3((unsigned)blocks), dim3(MP_THREADS), 0, stream, true,
+                              (float*)out, a, rows, width, lambda, eps, out_scale));
+  else
+    KVB_CHECK_CUDA(kvb_launch((maps_combine_kernel<bf16>), dim3((unsigned)blocks), dim3(MP_THREADS), 0, stream, true,
+                              (bf16*)out, a, rows, width, lambda, eps, out_scale));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ out, const T* __restrict__ o, long long o_token_stride,
+                                        long long o_head_stride, const T* __restrict__ g, long long g_stride,
+                                        long long count, int heads, int width) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GATE_MUL);
+  const long long step = (long long)gridDim.x * blockDim.x;
+  const int per_token = heads * width;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += step) {
+    const long long t = i / per_token;
+    const int c = (int)(i % per_token), h = c / width, j = c % width;
+    const float value = to_float(o[t * o_token_stride + (long long)h * o_head_stride + j]);
+    const float gate = to_float(g[t * g_stride + c]);
+    out[i] = from_float<T>(value / (1.0f + expf(-gate)));
+  }
+}
+
+extern "C" int kvb_sigmoid_gate_mul(void* out, const void* o, long long o_token_stride, long long o_head_stride,
+                                    const void* g, long long g_stride, int tokens, int heads, int width, int dtype,
+                                    cudaStream_t stream) {
+  const long long count = (long long)tokens * heads * width;
+  if (count == 0) return 0;
+  const int threads = 256;
+  const long long wanted = (count + threads - 1) / threads;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
+  const int blocks = (int)(wanted < resident ? wanted : resident);
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true,
+        (float*)out, (const float*)o, o_token_stride, o_head_stride, (const float*)g, g_stride, count, heads, width));
+  else
+    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true,
+        (bf16*)out, (const bf16*)o, o_token_stride, o_head_stride, (const bf16*)g, g_stride, count, heads, width));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+KVB_TRACE_TU(mixer_prepare)

@@ -141,7 +141,7 @@ class ModelRunner:
             max_model_len=self.max_model_len,
             # state that a mixer keeps per request cannot be taken over with the pages
             enable_prefix_caching=config.cache_config.enable_prefix_caching
-            and not any(req.state_spec is not None for req in requirements),
+            and not any(req.state_spec is not None or req.block_state_spec is not None for req in requirements),
             track_released_pages=config.cache_config.debug_fill_freed_pages is not None,
         )
         self.storage = CacheStorage(

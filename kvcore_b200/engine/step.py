@@ -49,6 +49,7 @@ class LayerCache:
     owner: bool
     state: torch.Tensor | None
     page_size: int
+    block_state: torch.Tensor | None = None   # ``[slots, *shape]`` of the block's own ``StateSpec``
 
     @property
     def k(self) -> torch.Tensor | None:
@@ -147,7 +148,12 @@ class CacheStorage:
                     (num_slots, *req.state_spec.shape), dtype=req.state_spec.dtype, device=device
                 )
                 self.state_tensors.append(state)
-            self.layer_caches.append(LayerCache(group_id, planes, owner, state, page_size))
+            block_state = None
+            if req.block_state_spec is not None:
+                block_state = torch.zeros((num_slots, *req.block_state_spec.shape),
+                                          dtype=req.block_state_spec.dtype, device=device)
+                self.state_tensors.append(block_state)
+            self.layer_caches.append(LayerCache(group_id, planes, owner, state, page_size, block_state))
 
     # what "poison" writes into freed pages: large enough that a read of a position nobody wrote
     # changes the logits by orders of magnitude, finite so that a masked probability of exactly

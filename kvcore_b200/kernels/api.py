@@ -69,6 +69,17 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
+        "kvb_rms_norm_shift": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _int, _vp],
+        "kvb_stream_add_norm": [_vp, _vp, _vp, _vp, _int, _int, _float, _vp, _vp, _ll, _vp, _int, _int, _int, _vp],
+        "kvb_attention_dims_rows": [_vp, _ll, _ll, _int, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp,
+                                    _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _float,
+                                    _int, _int, _vp],
+        "kvb_latent_prepare": [_vp, _ll, _vp, _float, _vp, _int, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _vp,
+                               _ll, _ll, _int, _vp, _ll, _ll, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_head_norm_kv_write": [_vp, _ll, _vp, _vp, _float, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _int,
+                                   _int, _int, _int, _int, _int, _vp],
+        "kvb_maps_combine": [_vp, _vp, _ll, _int, _float, _float, _float, _int, _vp],
+        "kvb_sigmoid_gate_mul": [_vp, _vp, _ll, _ll, _vp, _ll, _int, _int, _int, _int, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
@@ -639,12 +650,15 @@ STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 _stream_scratch: dict[int, torch.Tensor] = {}
 
 
-TRACE_TAGS = {25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_rows", 30: "latent_prepare",
+              31: "head_norm_kv_write", 32: "maps_combine", 33: "sigmoid_gate_mul", 34: "flash_dims",
+              35: "flash_dims_combine", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
-                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe", "attention_kept_first")
+                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe", "attention_kept_first",
+                "stream_norm", "attention_dims", "mixer_prepare")
 _trace_buffer: torch.Tensor | None = None
 
 
@@ -900,9 +914,11 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
     return out
 
 
-def stream_add(base: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tensor | None = None) -> torch.Tensor:
+def stream_add(base: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
     """The 32-bit residual stream: ``base + (a + b)`` summed in 32-bit.  A 32-bit ``base`` is updated in
-    place and returned; a ``base`` of the activation type (the embedded tokens) is widened into a new stream."""
+    place and returned; a ``base`` of the activation type (the embedded tokens) is widened into a new stream
+    (into ``out`` when given: a 32-bit tensor of the same shape)."""
     _check(base, "base")
     for name, t in (("a", a), ("b", b)):
         if t is not None:
@@ -911,13 +927,252 @@ def stream_add(base: torch.Tensor, a: torch.Tensor | None = None, b: torch.Tenso
                 raise KernelError(f"stream_add: {name} {tuple(t.shape)} does not match the stream {tuple(base.shape)}")
     if b is not None and (a is None or a.dtype != b.dtype):
         raise KernelError("stream_add: the two addends must have one type")
-    out = base if base.dtype == torch.float32 else torch.empty(base.shape, dtype=torch.float32, device=base.device)
-    if a is None and base.dtype == torch.float32:
+    if out is not None:
+        _check(out, "out", dtype=torch.float32)
+        if out.shape != base.shape:
+            raise KernelError(f"stream_add: out {tuple(out.shape)} does not match the stream {tuple(base.shape)}")
+    elif base.dtype == torch.float32:
+        out = base
+    else:
+        out = torch.empty(base.shape, dtype=torch.float32, device=base.device)
+    if a is None and out is base:
         return out
     addend = a if a is not None else base
     _call("kvb_stream_add", out.data_ptr(), base.data_ptr(), _dtype_code(base), None if a is None else a.data_ptr(),
           None if b is None else b.data_ptr(), base.numel(), _dtype_code(addend), _stream())
     return out
+
+
+def rms_norm_shift(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype | None = None, *,
+                   shift: torch.Tensor | None = None, state: torch.Tensor | None = None, ctx=None) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * weight`` over the rows of ``x [rows, width]`` (the 32-bit stream of a
+    bfloat16 model, or rows of the activation type) into ``out_dtype``.  With ``shift`` (``[width]``) every
+    normed row ``y_t`` becomes ``y_t + (y_{t-1} - y_t) * shift`` with ``y_{t-1}`` the normed row of the
+    request's token in front: the row before inside the step, else the request's row of ``state``
+    (``[slots, width]`` 32-bit, addressed by ``ctx.state_slots``), which this call also brings up to date."""
+    _check(x, "x")
+    _check(weight, "weight")
+    rows, width = x.shape
+    if weight.numel() != width:
+        raise KernelError(f"rms_norm_shift: weight has {weight.numel()} entries for rows of width {width}")
+    out = torch.empty((rows, width), dtype=out_dtype or x.dtype, device=x.device)
+    pointers = (None, None, None, None, None)
+    if shift is not None:
+        _check(shift, "shift", dtype=weight.dtype)
+        if state is None or ctx is None:
+            raise KernelError("rms_norm_shift: a token shift needs the state rows and the step's context")
+        _check(state, "state", dtype=torch.float32)
+        if shift.numel() != width or state.dim() != 2 or state.shape[1] != width:
+            raise KernelError(f"rms_norm_shift: shift {tuple(shift.shape)} / state {tuple(state.shape)} do not "
+                              f"match rows of width {width}")
+        pointers = (shift.data_ptr(), state.data_ptr(), ctx.req_index.data_ptr(), ctx.query_start.data_ptr(),
+                    ctx.state_slots.data_ptr())
+    _call("kvb_rms_norm_shift", out.data_ptr(), x.data_ptr(), weight.data_ptr(), *pointers, rows, width, float(eps),
+          _dtype_code(x), _dtype_code(out), _dtype_code(weight), _stream())
+    return out
+
+
+def stream_add_norm(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, *,
+                    out: torch.Tensor | None = None, stack: torch.Tensor | None = None, depth: int = 0,
+                    coeffs: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """``X = x + a * rsqrt(mean(a^2) + eps) * weight`` on the 32-bit stream ``x [rows, width]`` (``a``: a
+    sub-layer's output), into ``out`` (default: in place).  With ``coeffs`` (``[depth + 1]``) it also returns
+    the weighted average ``sum_{j < depth} coeffs[j] * stack[j] + coeffs[depth] * X`` over the results in
+    front (``stack [>= depth, rows, width]`` 32-bit); returns ``(X, average or None)``."""
+    _check(x, "x", dtype=torch.float32)
+    _check(a, "a")
+    _check(weight, "weight")
+    rows, width = x.shape
+    if a.shape != x.shape or weight.numel() != width:
+        raise KernelError(f"stream_add_norm: a {tuple(a.shape)} / weight do not match the stream {tuple(x.shape)}")
+    out = x if out is None else out
+    _check(out, "out", dtype=torch.float32)
+    if out.shape != x.shape:
+        raise KernelError("stream_add_norm: out does not match the stream")
+    avg = None
+    extra = (None, None, 0, None, 0)
+    if coeffs is not None:
+        _check(coeffs, "coeffs", dtype=weight.dtype)
+        if coeffs.numel() != depth + 1:
+            raise KernelError(f"stream_add_norm: {coeffs.numel()} coefficients for {depth} results in front and one new")
+        if depth:
+            if stack is None:
+                raise KernelError("stream_add_norm: the results in front are missing")
+            _check(stack, "stack", dtype=torch.float32)
+            if stack.dim() != 3 or stack.shape[0] < depth or tuple(stack.shape[1:]) != (rows, width):
+                raise KernelError(f"stream_add_norm: stack {tuple(stack.shape)} does not hold {depth} x {tuple(x.shape)}")
+        avg = torch.empty_like(x)
+        extra = (avg.data_ptr(), None if not depth else stack.data_ptr(), rows * width, coeffs.data_ptr(), depth)
+    _call("kvb_stream_add_norm", out.data_ptr(), x.data_ptr(), a.data_ptr(), weight.data_ptr(), rows, width,
+          float(eps), *extra, _dtype_code(a), _dtype_code(weight), _stream())
+    return out, avg
+
+
+def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, table: torch.Tensor, ctx, *,
+                   value_heads: int, group: int, maps: int, key_width: int, value_width: int, page_size: int,
+                   num_pages: int, key_strides: tuple[int, int, int], value_strides: tuple[int, int, int], scale: float,
+                   sink: torch.Tensor | None = None, window: int | None = None,
+                   out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                   force_general: bool = False, num_splits: int | None = None) -> torch.Tensor:
+    """Paged attention with a key width and a value width of their own.
+
+    ``q [T, HQ, key_width]`` (a view; last stride 1) with ``HQ = value_heads * group * maps``: query head
+    ``hq`` reads value head ``hq // (group * maps)`` and key head ``vh * maps + hq % maps``.  ``keys`` and
+    ``values`` are tensors inside the paged cache (they may be views of one plane, and ``values`` may be a
+    view of ``keys``); ``key_strides`` / ``value_strides`` give their (page, head, row) strides in elements;
+    page ``p`` slot ``s`` head ``h`` starts at ``p * page + h * head + s * row``.  ``sink [HQ]`` (32-bit):
+    a logit per query head that joins the softmax's denominator.  Returns ``[T, HQ, value_width]`` in
+    ``out_dtype`` (32-bit or the cache's type; default the cache's) or fills ``out`` (a view with last
+    stride 1).  bfloat16 shapes the tensor-core kernel takes run there; everything else, and all of float32,
+    on the general kernel."""
+    _check(q, "q", contiguous=False)
+    _check(keys, "keys", dtype=q.dtype, contiguous=False)
+    _check(values, "values", dtype=q.dtype, contiguous=False)
+    _check(table, "block table", dtype=torch.int32, contiguous=False)
+    tokens, hq, dk = q.shape
+    if dk != key_width or hq != value_heads * group * maps or q.stride(2) != 1:
+        raise KernelError(f"attention_dims: q {tuple(q.shape)} does not match {value_heads} x {group} x {maps} heads "
+                          f"of width {key_width}")
+    if out is None:
+        out = torch.empty((tokens, hq, value_width), dtype=out_dtype or q.dtype, device=q.device)
+    if tuple(out.shape) != (tokens, hq, value_width) or out.stride(2) != 1 or out.dtype not in (torch.float32, q.dtype):
+        raise KernelError(f"attention_dims: out {tuple(out.shape)} {out.dtype} does not fit")
+    if sink is not None:
+        _check(sink, "sink", dtype=torch.float32)
+        if sink.numel() != hq:
+            raise KernelError(f"attention_dims: {sink.numel()} sinks for {hq} query heads")
+    if tokens == 0:
+        return out
+    if (not force_general and flash_dims_supported(q, out, key_width, value_width, page_size, key_strides,
+                                                    value_strides, keys, values)):
+        _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
+                    num_pages, key_strides, value_strides, scale, sink, window, num_splits)
+        return out
+    _call("kvb_attention_dims_rows", out.data_ptr(), out.stride(0), out.stride(1), int(out.dtype == torch.float32),
+          q.data_ptr(), q.stride(0), q.stride(1), keys.data_ptr(), *key_strides, values.data_ptr(), *value_strides,
+          table.data_ptr(), table.stride(0), ctx.positions.data_ptr(), ctx.req_index.data_ptr(),
+          None if sink is None else sink.data_ptr(), tokens, hq, group * maps, maps, key_width, value_width,
+          page_size, num_pages, float(scale), int(window or 0), _dtype_code(q), _stream())
+    return out
+
+
+def flash_dims_supported(q, out, key_width, value_width, page_size, key_strides, value_strides, keys, values) -> bool:
+    """Whether the tensor-core kernel for separate key and value widths takes this call."""
+    return False
+
+
+def latent_prepare(kv_rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, dims: int,
+                   ctx, table: torch.Tensor, cache: torch.Tensor, q: torch.Tensor, q_width: int,
+                   q_out: torch.Tensor, *, q_latent: torch.Tensor | None = None, write: bool = True) -> None:
+    """Between the projections and the attention of a mixer that caches one latent vector a token.
+
+    ``kv_rows [T, rank + rot]`` (a view): the first ``rank`` entries get an RMS norm with ``norm_weight``, the
+    first ``dims`` of the last ``rot`` are turned by the token's position (entry 2i with 2i+1, angle
+    ``position * inv_freq[i]``); the row goes into the token's place of ``cache [pages, 1, page, rank + rot]``
+    if ``write``.  ``q [T, H, q_width + rot]`` (a view): its last ``rot`` entries, turned the same way, go
+    behind the first ``rank`` entries of ``q_out [T, H, rank + rot]``; those first entries are copied from
+    ``q_latent [T, H, rank]`` (a view) when given."""
+    _check(kv_rows, "kv_rows", contiguous=False)
+    _check(q, "q", dtype=kv_rows.dtype, contiguous=False)
+    _check(q_out, "q_out", dtype=kv_rows.dtype)
+    _check(cache, "cache", dtype=kv_rows.dtype)
+    _check(norm_weight, "norm_weight", dtype=kv_rows.dtype)
+    _check(inv_freq, "inv_freq", dtype=torch.float32)
+    tokens, heads, row = q_out.shape
+    rank = norm_weight.numel()
+    rot = row - rank
+    num_pages, one, page_size, width = cache.shape
+    if (one, width) != (1, row) or tuple(kv_rows.shape) != (tokens, row) or tuple(q.shape) != (tokens, heads, q_width + rot):
+        raise KernelError(f"latent_prepare: shapes kv_rows {tuple(kv_rows.shape)}, q {tuple(q.shape)}, q_out "
+                          f"{tuple(q_out.shape)}, cache {tuple(cache.shape)} do not fit")
+    if kv_rows.stride(1) != 1 or q.stride(2) != 1 or inv_freq.numel() * 2 < dims:
+        raise KernelError("latent_prepare: rows must be contiguous in their last axis")
+    latent = (None, 0, 0)
+    if q_latent is not None:
+        _check(q_latent, "q_latent", dtype=kv_rows.dtype, contiguous=False)
+        if tuple(q_latent.shape) != (tokens, heads, rank) or q_latent.stride(2) != 1:
+            raise KernelError(f"latent_prepare: q_latent {tuple(q_latent.shape)} does not fit")
+        latent = (q_latent.data_ptr(), q_latent.stride(0), q_latent.stride(1))
+    _call("kvb_latent_prepare", kv_rows.data_ptr(), kv_rows.stride(0), norm_weight.data_ptr(), float(eps),
+          inv_freq.data_ptr(), int(dims), ctx.positions.data_ptr(), ctx.req_index.data_ptr(), table.data_ptr(),
+          table.stride(0), cache.data_ptr(), page_size, num_pages, int(write), q.data_ptr(), q.stride(0), q.stride(1),
+          int(q_width), *latent, q_out.data_ptr(), tokens, heads, rank, rot, _dtype_code(kv_rows), _stream())
+
+
+def head_norm_kv_write(rows: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor | None, eps: float, ctx,
+                       table: torch.Tensor, cache: torch.Tensor, *, q_vectors: int, k_vectors: int, dim: int,
+                       value_width: int, write: bool = True) -> None:
+    """``rows [T, (q_vectors + k_vectors) * dim + value_width]`` (a view; without the k and v part when not
+    ``write``): every q and k vector of ``dim`` entries gets an RMS norm of its own (weights ``[dim]``, shared);
+    q in place, the normed k vectors and the values side by side into the token's row of
+    ``cache [pages, 1, page, k_vectors * dim + value_width]``."""
+    _check(rows, "rows", contiguous=False)
+    _check(q_weight, "q_weight", dtype=rows.dtype)
+    _check(cache, "cache", dtype=rows.dtype)
+    tokens = rows.shape[0]
+    num_pages, one, page_size, width = cache.shape
+    need = q_vectors * dim + ((k_vectors * dim + value_width) if write else 0)
+    if rows.stride(1) != 1 or rows.shape[1] < need or (one, width) != (1, k_vectors * dim + value_width):
+        raise KernelError(f"head_norm_kv_write: rows {tuple(rows.shape)} / cache {tuple(cache.shape)} do not fit")
+    if write:
+        _check(k_weight, "k_weight", dtype=rows.dtype)
+    _call("kvb_head_norm_kv_write", rows.data_ptr(), rows.stride(0), q_weight.data_ptr(),
+          None if k_weight is None else k_weight.data_ptr(), float(eps), ctx.positions.data_ptr(),
+          ctx.req_index.data_ptr(), table.data_ptr(), table.stride(0), cache.data_ptr(), page_size, num_pages,
+          int(write), tokens, q_vectors, k_vectors, dim, value_width, _dtype_code(rows), _stream())
+
+
+def maps_combine(a: torch.Tensor, lam: float, eps: float, out_scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``a [T, H, 2, width]`` (32-bit: the outputs of a head's two score maps) -> ``[T, H * width]`` in
+    ``out_dtype``: ``o = a[..., 0, :] - lam * a[..., 1, :]``, divided by its root mean square over ``width``
+    (eps inside the root), times ``out_scale``."""
+    _check(a, "a", dtype=torch.float32)
+    tokens, heads, two, width = a.shape
+    if two != 2:
+        raise KernelError(f"maps_combine: two maps a head, got {tuple(a.shape)}")
+    out = torch.empty((tokens, heads * width), dtype=out_dtype, device=a.device)
+    _call("kvb_maps_combine", out.data_ptr(), a.data_ptr(), tokens * heads, width, float(lam), float(eps),
+          float(out_scale), _dtype_code(out), _stream())
+    return out
+
+
+def sigmoid_gate_mul(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``o [T, H, width]`` (a view) times ``sigmoid(gate [T, H * width])`` (a view of rows) -> ``[T, H * width]``."""
+    _check(o, "o", contiguous=False)
+    _check(gate, "gate", dtype=o.dtype, contiguous=False)
+    tokens, heads, width = o.shape
+    if o.stride(2) != 1 or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, heads * width):
+        raise KernelError(f"sigmoid_gate_mul: o {tuple(o.shape)} and gate {tuple(gate.shape)} do not fit")
+    out = torch.empty((tokens, heads * width), dtype=o.dtype, device=o.device)
+    _call("kvb_sigmoid_gate_mul", out.data_ptr(), o.data_ptr(), o.stride(0), o.stride(1), gate.data_ptr(),
+          gate.stride(0), tokens, heads, width, _dtype_code(o), _stream())
+    return out
+
+
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """A product per head: ``x [T, H, K]`` (a view; last stride 1) with ``weight [H, N, K]`` -> ``[T, H, N]``
+    (a view when the batched library product made it; into ``out``, a view with last stride 1, on the 32-bit
+    path).  float32: this package's own FMA kernel, head by head; bfloat16: one batched library product."""
+    _check(x, "x", contiguous=False)
+    _check(weight, "weight", dtype=x.dtype)
+    tokens, heads, k = x.shape
+    if weight.dim() != 3 or weight.shape[0] != heads or weight.shape[2] != k or x.stride(2) != 1:
+        raise KernelError(f"heads_linear: x {tuple(x.shape)} does not match weight {tuple(weight.shape)}")
+    n = weight.shape[1]
+    if x.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((tokens, heads, n), dtype=torch.float32, device=x.device)
+        if tuple(out.shape) != (tokens, heads, n) or out.stride(2) != 1:
+            raise KernelError(f"heads_linear: out {tuple(out.shape)} does not fit")
+        for h in range(heads):
+            _call("kvb_gemm_f32", out[:, h].data_ptr(), x[:, h].data_ptr(), weight[h].data_ptr(), None, tokens, n, k,
+                  x.stride(0), out.stride(0), _stream())
+        return out
+    result = torch.bmm(x.transpose(0, 1), weight.transpose(1, 2)).transpose(0, 1)
+    if out is not None:
+        out.copy_(result)
+        return out
+    return result
 
 
 QK_NORM_MODES = {None: 0, "none": 0, "projection": 1, "head": 2}

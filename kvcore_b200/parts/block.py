@@ -1,5 +1,5 @@
-"""Arrangements of one layer: pre-norm mixer and feed-forward in sequence on a deferred residual, or side
-by side on a 32-bit stream.
+"""Arrangements of one layer: pre-norm mixer and feed-forward in sequence on a deferred residual, side
+by side on a 32-bit stream, or in sequence on a 32-bit stream with a norm on both sides of each.
 
 As the reference's decoder layer (kvcore/model/models/llama3.py:124-142): the running
 ``residual`` and the last sub-layer output ``h`` stay separate and are summed inside the
@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels as K
 from ..config.model_spec import LayerSpec
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Summed, WeightSlot
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, StateSpec, Summed, WeightSlot
 
 
 class PreNormResidualBlock(Block):
@@ -120,7 +120,108 @@ class ParallelResidualBlock(Block):
         return Summed(None), K.stream_add(stream, a, f)
 
 
+class SandwichResidualBlock(Block):
+    """A norm before and after each sub-layer on one 32-bit stream:
+    ``x <- x + norm_b(mixer(norm_a(x)))`` and then ``x <- x + norm_d(ff(norm_c(x)))`` (a layer may have no
+    feed-forward).  The four norms are RMS scales (``as_rms_scale``), so each pair of steps around a sub-layer
+    is one kernel: norm (+ token shift) in front, norm + sum (+ depth average) behind.
+
+    Two optional mechanisms, each with its constants as parameters:
+
+    * ``token_shift`` (the name of a ``[width]`` tensor): what the mixer reads, ``y = norm_a(x)``, becomes
+      ``y_t + (y_{t-1} - y_t) * shift`` with ``y_{t-1}`` the unshifted normed row of the token in front (zeros
+      for a request's first token).  The last normed row of a request is per-request state of the block
+      (``state_spec``), kept in 32-bit.
+    * ``depth_average`` (the name of a ``[depth + 1]`` tensor) with ``depth`` results in front of this layer
+      (the embedded tokens and the results of the layers before it) out of ``depth_slots`` in the model: the
+      layer's result ``X`` joins them, and what goes on to the next layer is
+      ``sum_j c[j] * X_j + c[depth] * X``.  The results of a step live in one ``[depth_slots, T, width]``
+      32-bit tensor shared through the step's context.
+
+    In the ``(h, residual)`` pair that runs through the blocks this block returns ``(Summed, stream)``."""
+
+    def __init__(self, *, layer: LayerSpec, hidden_size: int, token_shift: str | None = None,
+                 depth_average: str | None = None, depth: int = 0, depth_slots: int = 0,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        self.hidden_size = int(hidden_size)
+        self.dtype = dtype
+        norms = layer.norms
+        self.mixer_norm = NORMS.build(norms["mixer_norm"], dtype=dtype, device=device)
+        self.mixer_out_norm = NORMS.build(norms["mixer_out_norm"], dtype=dtype, device=device)
+        self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_out_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(norms["feed_forward_norm"], dtype=dtype, device=device)
+            self.feed_forward_out_norm = NORMS.build(norms["feed_forward_out_norm"], dtype=dtype, device=device)
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
+        for norm in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
+            if norm is not None and norm.as_rms_scale() is None:
+                raise ValueError("a sandwich block fuses its norms with the sums around them: they must be RMS scales")
+        self.shift_tensor, self.average_tensor = token_shift, depth_average
+        self.shift = torch.empty(self.hidden_size, dtype=dtype, device=device) if token_shift else None
+        self.depth, self.depth_slots = int(depth), int(depth_slots)
+        self.average = None
+        if depth_average:
+            if not 0 < self.depth < self.depth_slots:
+                raise ValueError(f"a depth average over {self.depth} results in front needs 0 < depth < depth_slots "
+                                 f"({self.depth_slots})")
+            self.average = torch.empty(self.depth + 1, dtype=dtype, device=device)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.feed_forward_norm,
+                                 self.feed_forward, self.feed_forward_out_norm) if p is not None)
+
+    graph_safe = PreNormResidualBlock.graph_safe
+    ignorable_tensor_names = PreNormResidualBlock.ignorable_tensor_names
+    finalize_weights = PreNormResidualBlock.finalize_weights
+
+    def weight_slots(self) -> list[WeightSlot]:
+        slots = PreNormResidualBlock.weight_slots(self)
+        if self.shift is not None:
+            slots.append(WeightSlot(self.shift_tensor, self.shift, init="normal"))
+        if self.average is not None:
+            slots.append(WeightSlot(self.average_tensor, self.average, init="normal"))
+        return slots
+
+    def state_spec(self) -> StateSpec | None:
+        """The block's own per-request state: the last normed row the mixer's shift has seen."""
+        return StateSpec((self.hidden_size,), torch.float32) if self.shift is not None else None
+
+    def forward(self, h, residual, ctx, cache):
+        stack = None
+        if self.average is not None:
+            stack = ctx.shared(("depth_results", self.depth_slots, self.hidden_size), lambda: torch.empty(
+                (self.depth_slots, ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=h.device))
+        if residual is None:                      # the embedded tokens start the stream (and are result 0)
+            x = K.stream_add(h, out=None if stack is None else stack[0])
+        else:
+            x = residual if residual.dtype == torch.float32 else K.stream_add(residual)
+            if not isinstance(h, Summed):
+                x = K.stream_add(x, h)
+            if stack is not None and self.depth == 1:
+                stack[0].copy_(x)                  # a block of another kind stood in front: its result is result 0
+        weight, eps = self.mixer_norm.as_rms_scale()
+        y = K.rms_norm_shift(x, weight, eps, self.dtype, shift=self.shift,
+                             state=None if self.shift is None else cache.block_state, ctx=ctx)
+        a = self.mixer.forward(y, ctx, cache)
+        weight, eps = self.mixer_out_norm.as_rms_scale()
+        # the layer's result goes to its place among the results when they are averaged; the stream handed
+        # in is then left as it was (it may be a result itself)
+        place = None if stack is None else stack[self.depth]
+        average = dict(stack=stack, depth=self.depth, coeffs=self.average) if stack is not None else {}
+        if self.feed_forward is None:
+            result, mean = K.stream_add_norm(x, a, weight, eps, out=place, **average)
+            return Summed(None), (result if mean is None else mean)
+        x, _ = K.stream_add_norm(x, a, weight, eps, out=place)
+        weight, eps = self.feed_forward_norm.as_rms_scale()
+        f = self.feed_forward.forward(K.rms_norm_shift(x, weight, eps, self.dtype), ctx)
+        weight, eps = self.feed_forward_out_norm.as_rms_scale()
+        result, mean = K.stream_add_norm(x, f, weight, eps, **average)
+        return Summed(None), (result if mean is None else mean)
+
+
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("sandwich_residual", SandwichResidualBlock)
 BLOCKS.register("parallel_residual", ParallelResidualBlock)
 
-__all__ = ["ParallelResidualBlock", "PreNormResidualBlock"]
+__all__ = ["ParallelResidualBlock", "PreNormResidualBlock", "SandwichResidualBlock"]

@@ -43,6 +43,7 @@ class LMHead(Part):
         tied_to: str | None = None,
         logit_scale: float = 1.0,
         tied_weight: torch.Tensor | None = None,
+        tensor: str | None = None,
         dtype,
         device,
     ) -> None:
@@ -51,6 +52,7 @@ class LMHead(Part):
         self.name = name
         self.tied_to = tied_to
         self.logit_scale = float(logit_scale)
+        self.tensor = tensor or f"{name}.weight"     # the matrix's full checkpoint name
         if tied_to is not None:
             if tied_weight is None:
                 raise ValueError(f"lm head is tied to {tied_to!r} but no such matrix was given")
@@ -61,11 +63,11 @@ class LMHead(Part):
     def weight_slots(self) -> list[WeightSlot]:
         if self.tied_to is not None:
             return []
-        return [WeightSlot(f"{self.name}.weight", self.weight)]
+        return [WeightSlot(self.tensor, self.weight)]
 
     def ignorable_tensor_names(self) -> list[str]:
         # a checkpoint may still carry the tied matrix under the head's own name
-        return [f"{self.name}.weight"] if self.tied_to is not None else []
+        return [self.tensor] if self.tied_to is not None else []
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
         logits = K.linear(hidden, self.weight, None, out_dtype=torch.float32)

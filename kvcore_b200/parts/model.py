@@ -13,7 +13,7 @@ import torch
 
 from .. import kernels as K
 from ..config.model_spec import ModelSpec
-from . import attention, block, embedding, mlp, moe, norm, rope  # noqa: F401  (register the stock parts)
+from . import attention, attention_maps, block, embedding, mlp, moe, norm, rope  # noqa: F401  (register the stock parts)
 from .base import BLOCKS, EMBEDDINGS, LM_HEADS, NORMS, CacheSpec, StateSpec, Summed, WeightSlot
 
 
@@ -26,6 +26,7 @@ class EntryRequirement:
     cache_spec: CacheSpec | None
     state_spec: StateSpec | None
     cache_of: int | None
+    block_state_spec: StateSpec | None = None   # per-request state the block itself keeps (a token shift)
 
 
 class DecoderModel:
@@ -93,9 +94,12 @@ class DecoderModel:
     def entry_requirements(self) -> list[EntryRequirement]:
         out = []
         for index, entry in enumerate(self.schedule):
-            mixer = self.blocks[entry.layer].mixer
+            block = self.blocks[entry.layer]
+            mixer = block.mixer
+            block_state = getattr(block, "state_spec", None)
             out.append(
-                EntryRequirement(index, entry.layer, mixer.cache_spec(), mixer.state_spec(), entry.cache_of)
+                EntryRequirement(index, entry.layer, mixer.cache_spec(), mixer.state_spec(), entry.cache_of,
+                                 None if block_state is None else block_state())
             )
         return out
 

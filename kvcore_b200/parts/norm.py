@@ -73,7 +73,38 @@ class LayerNorm(Norm):
         return self.forward(residual), residual
 
 
+class RMSNormStream(Norm):
+    """``x * rsqrt(mean(x^2) + eps) * weight`` over rows of a 32-bit residual stream (or of the activation
+    type), written in the activation type; statistics and scaling in 32-bit.  ``tensor`` is the weight's full
+    checkpoint name (default ``<name>.weight``)."""
+
+    graph_safe = True
+
+    def __init__(self, *, size: int, eps: float, name: str, tensor: str | None = None,
+                 dtype: torch.dtype, device: torch.device):
+        self.size = int(size)
+        self.eps = float(eps)
+        self.name = name
+        self.dtype = dtype
+        self.tensor = tensor or f"{name}.weight"
+        self.weight = torch.empty(self.size, dtype=dtype, device=device)
+
+    def weight_slots(self) -> list[WeightSlot]:
+        return [WeightSlot(self.tensor, self.weight, init="ones")]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return K.rms_norm_shift(x, self.weight, self.eps, self.dtype)
+
+    def forward_residual(self, h: torch.Tensor, residual: torch.Tensor):
+        residual = K.stream_add(residual, h) if residual.dtype == torch.float32 else residual.add_(h)
+        return self.forward(residual), residual
+
+    def as_rms_scale(self):
+        return self.weight, self.eps
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("rmsnorm_stream", RMSNormStream)
 NORMS.register("layernorm", LayerNorm)
 
-__all__ = ["LayerNorm", "RMSNorm"]
+__all__ = ["LayerNorm", "RMSNorm", "RMSNormStream"]

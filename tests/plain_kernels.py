@@ -160,12 +160,154 @@ def layer_norm(x, weight, bias, eps, out_dtype=None):
     return y.to(out_dtype or x.dtype)
 
 
-def stream_add(base, a=None, b=None):
-    out = base if base.dtype == torch.float32 else base.float()
+def stream_add(base, a=None, b=None, out=None):
+    if out is not None:
+        out.copy_(base.float())
+    else:
+        out = base if base.dtype == torch.float32 else base.float()
     if a is not None:
         addend = a.float() if b is None else a.float() + b.float()
-        out = out.add_(addend) if out is base else out + addend
+        out = out.add_(addend) if (out is base or out.data_ptr() != base.data_ptr()) else out + addend
     return out
+
+
+def _rms(x, eps):
+    xf = x.float()
+    return xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def rms_norm_shift(x, weight, eps, out_dtype=None, *, shift=None, state=None, ctx=None):
+    y = _rms(x, eps) * weight.float()
+    if shift is not None:
+        before = torch.empty_like(y)
+        starts = [int(v) for v in ctx.query_start]
+        for r in range(ctx.num_reqs):
+            lo, hi = starts[r], starts[r + 1]
+            slot = int(ctx.state_slots[r])
+            before[lo] = state[slot]
+            before[lo + 1:hi] = y[lo:hi - 1]
+            state[slot] = y[hi - 1]
+        y = y + (before - y) * shift.float()
+    return y.to(out_dtype or x.dtype)
+
+
+def stream_add_norm(x, a, weight, eps, *, out=None, stack=None, depth=0, coeffs=None):
+    result = x + _rms(a, eps) * weight.float()
+    if out is None:
+        out = x
+    out.copy_(result)
+    avg = None
+    if coeffs is not None:
+        avg = torch.zeros_like(result)
+        for j in range(depth):
+            avg = avg + coeffs[j].float() * stack[j]
+        avg = avg + coeffs[depth].float() * result
+    return out, avg
+
+
+def _strided(tensor, page, slot, head, strides, width):
+    """The ``width`` entries of (page, head, slot) inside the cache tensor ``tensor`` (a view into it)."""
+    begin = page * strides[0] + head * strides[1] + slot * strides[2]
+    return tensor.reshape(-1)[begin:begin + width] if tensor.is_contiguous() else \
+        torch.as_strided(tensor, (width,), (1,), tensor.storage_offset() + begin)
+
+
+def attention_dims(q, keys, values, table, ctx, *, value_heads, group, maps, key_width, value_width, page_size,
+                   num_pages, key_strides, value_strides, scale, sink=None, window=None, out=None, out_dtype=None,
+                   force_general=False, num_splits=None):
+    tokens, hq, _ = q.shape
+    if out is None:
+        out = torch.empty((tokens, hq, value_width), dtype=out_dtype or q.dtype, device=q.device)
+    flat_k = torch.as_strided(keys, (keys.untyped_storage().nbytes() // keys.element_size() - keys.storage_offset(),), (1,),
+                              keys.storage_offset())
+    flat_v = torch.as_strided(values, (values.untyped_storage().nbytes() // values.element_size() - values.storage_offset(),),
+                              (1,), values.storage_offset())
+    for t in range(tokens):
+        pos = int(ctx.positions[t])
+        first = 0 if not window else max(0, pos - window + 1)
+        positions = torch.arange(first, pos + 1)
+        pages = table[int(ctx.req_index[t])].long()[positions // page_size]
+        assert bool((pages > 0).all()) and bool((pages < num_pages).all()), "read through a page that is not held"
+        slots = positions % page_size
+        for h in range(hq):
+            vh = h // (group * maps)
+            kh = vh * maps + h % maps
+            k_begin = pages * key_strides[0] + kh * key_strides[1] + slots * key_strides[2]
+            v_begin = pages * value_strides[0] + vh * value_strides[1] + slots * value_strides[2]
+            k = flat_k[k_begin[:, None] + torch.arange(key_width)[None]].float()
+            v = flat_v[v_begin[:, None] + torch.arange(value_width)[None]].float()
+            scores = (k @ q[t, h].float()) * scale
+            top = scores.max() if sink is None else torch.maximum(scores.max(), sink[h])
+            weights = torch.exp(scores - top)
+            total = weights.sum() + (0.0 if sink is None else torch.exp(sink[h] - top))
+            out[t, h] = ((weights / total) @ v).to(out.dtype)
+    return out
+
+
+def latent_prepare(kv_rows, norm_weight, eps, inv_freq, dims, ctx, table, cache, q, q_width, q_out, *,
+                   q_latent=None, write=True):
+    tokens, heads, row = q_out.shape
+    rank = norm_weight.numel()
+    rot = row - rank
+    page_size = cache.shape[2]
+
+    def turn(x, pos):          # [..., rot] float, interleaved pairs of the first ``dims`` entries
+        x = x.clone()
+        angle = torch.tensor(float(pos), dtype=torch.float32) * inv_freq[: dims // 2]
+        c, s = torch.cos(angle), torch.sin(angle)
+        u, v = x[..., 0:dims:2].clone(), x[..., 1:dims:2].clone()
+        x[..., 0:dims:2] = u * c - v * s
+        x[..., 1:dims:2] = v * c + u * s
+        return x
+
+    for t in range(tokens):
+        pos = int(ctx.positions[t])
+        if write:
+            page = int(table[int(ctx.req_index[t]), pos // page_size])
+            assert page > 0
+            latent = _rms(kv_rows[t, :rank], eps) * norm_weight.float()
+            cache[page, 0, pos % page_size, :rank] = latent.to(cache.dtype)
+            cache[page, 0, pos % page_size, rank:] = turn(kv_rows[t, rank:].float(), pos).to(cache.dtype)
+        q_out[t, :, rank:] = turn(q[t, :, q_width:].float(), pos).to(q_out.dtype)
+        if q_latent is not None:
+            q_out[t, :, :rank] = q_latent[t]
+
+
+def head_norm_kv_write(rows, q_weight, k_weight, eps, ctx, table, cache, *, q_vectors, k_vectors, dim, value_width,
+                       write=True):
+    tokens = rows.shape[0]
+    page_size = cache.shape[2]
+    qc, kc = q_vectors * dim, k_vectors * dim
+    q = rows[:, :qc].reshape(tokens, q_vectors, dim)
+    rows[:, :qc] = (_rms(q, eps) * q_weight.float()).to(rows.dtype).reshape(tokens, qc)
+    if not write:
+        return
+    k = (_rms(rows[:, qc:qc + kc].reshape(tokens, k_vectors, dim), eps) * k_weight.float()).to(rows.dtype)
+    for t in range(tokens):
+        pos = int(ctx.positions[t])
+        page = int(table[int(ctx.req_index[t]), pos // page_size])
+        assert page > 0
+        cache[page, 0, pos % page_size, :kc] = k[t].reshape(kc)
+        cache[page, 0, pos % page_size, kc:] = rows[t, qc + kc:qc + kc + value_width]
+
+
+def maps_combine(a, lam, eps, out_scale, out_dtype):
+    tokens, heads, _, width = a.shape
+    o = a[:, :, 0] - lam * a[:, :, 1]
+    return (_rms(o, eps) * out_scale).to(out_dtype).reshape(tokens, heads * width)
+
+
+def sigmoid_gate_mul(o, gate):
+    tokens, heads, width = o.shape
+    return (o.float().reshape(tokens, heads * width) * torch.sigmoid(gate.float())).to(o.dtype)
+
+
+def heads_linear(x, weight, out=None):
+    result = torch.einsum("thk,hnk->thn", x.float(), weight.float()).to(x.dtype)
+    if out is not None:
+        out.copy_(result)
+        return out
+    return result
 
 
 def qk_prepare(rows, positions, req_index, cos_sin, table, k_cache, v_cache, num_heads, num_kv_heads, head_dim, *,
@@ -342,6 +484,8 @@ def sample(logits, packed_params, eps):
 _NAMES = [
     "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "feed_tokens", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
+    "rms_norm_shift", "stream_add_norm", "attention_dims", "latent_prepare", "head_norm_kv_write", "maps_combine",
+    "sigmoid_gate_mul", "heads_linear",
     "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
 ]
 

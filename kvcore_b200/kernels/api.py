@@ -74,6 +74,9 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_attention_dims_rows": [_vp, _ll, _ll, _int, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp,
                                     _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _float,
                                     _int, _int, _vp],
+        "kvb_flash_dims_attention": [_vp, _ll, _ll, _int, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp,
+                                     _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _int,
+                                     _float, _int, _int, _vp, _vp],
         "kvb_latent_prepare": [_vp, _ll, _vp, _float, _vp, _int, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _vp,
                                _ll, _ll, _int, _vp, _ll, _ll, _vp, _int, _int, _int, _int, _int, _vp],
         "kvb_head_norm_kv_write": [_vp, _ll, _vp, _vp, _float, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _int,
@@ -658,7 +661,7 @@ TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_r
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
                 "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe", "attention_kept_first",
-                "stream_norm", "attention_dims", "mixer_prepare")
+                "stream_norm", "attention_dims", "mixer_prepare", "attention_flash_dims")
 _trace_buffer: torch.Tensor | None = None
 
 
@@ -1044,7 +1047,7 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
     if tokens == 0:
         return out
     if (not force_general and flash_dims_supported(q, out, key_width, value_width, page_size, key_strides,
-                                                    value_strides, keys, values)):
+                                                    value_strides, keys, values, maps)):
         _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
                     num_pages, key_strides, value_strides, scale, sink, window, num_splits)
         return out
@@ -1056,9 +1059,80 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
     return out
 
 
-def flash_dims_supported(q, out, key_width, value_width, page_size, key_strides, value_strides, keys, values) -> bool:
-    """Whether the tensor-core kernel for separate key and value widths takes this call."""
-    return False
+def _flash_dims_geometry(key_width: int, value_width: int, split_mode: bool, values_in_keys: bool):
+    """(value width a block accumulates, slices of the value width, shared-memory bytes) of the tensor-core
+    kernel for separate key and value widths, or None when it does not take them."""
+    if key_width % 16 or not 16 <= key_width <= 1024 or value_width % 8 or not 8 <= value_width <= 1024:
+        return None
+    slices = -(-value_width // 256)
+    each = -(-value_width // slices)
+    block = next((w for w in (32, 64, 96, 128, 192, 256) if w >= each), None)
+    if block is None:
+        return None
+    values_in_keys = values_in_keys and slices * block <= key_width
+    keys_per_tile = 64 if split_mode or key_width <= 256 else 32
+    tile_m = 16 if split_mode else 64
+    smem = 4 * keys_per_tile * 8 + (tile_m + 2 * keys_per_tile) * (key_width + 8) * 2
+    if not values_in_keys:
+        smem += 2 * keys_per_tile * (block + 8) * 2
+    if split_mode:
+        smem = max(smem, 4 * keys_per_tile * 8 + tile_m * (key_width + 8) * 2 + (4 * 16 * block + 128) * 4)
+    return (block, slices, smem) if smem <= 227 * 1024 else None
+
+
+def flash_dims_supported(q, out, key_width, value_width, page_size, key_strides, value_strides, keys, values,
+                         maps: int = 1) -> bool:
+    """Whether the tensor-core kernel for separate key and value widths takes this call: bfloat16, widths in
+    steps of 16 (keys) and 8 (values), every row on a 16-byte boundary, tiles that fit in shared memory."""
+    if q.dtype != torch.bfloat16:
+        return False
+    strides = (*key_strides, *value_strides, q.stride(0), q.stride(1))
+    if any(stride % 8 for stride in strides) or any(t.data_ptr() % 16 for t in (q, keys, values)):
+        return False
+    if out.stride(0) % 2 or out.stride(1) % 2 or out.data_ptr() % 8:
+        return False
+    alias = (keys.data_ptr() == values.data_ptr() and tuple(key_strides) == tuple(value_strides) and maps == 1)
+    return (_flash_dims_geometry(key_width, value_width, False, alias) is not None
+            and _flash_dims_geometry(key_width, value_width, True, alias) is not None)
+
+
+def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
+                num_pages, key_strides, value_strides, scale, sink, window, num_splits) -> None:
+    """The tensor-core kernel on the step's batch.  A mixed step (portions of prompts beside single decoded
+    tokens, longest first as the step function packs them) goes as two runs of requests, so that the
+    decoded tokens take the shape made for few rows and have their keys cut into chunks."""
+    lens = getattr(ctx, "host_query_lens", None)
+    contexts = getattr(ctx, "host_context_lens", None)
+    runs = [(ctx, table)]
+    if num_splits is None and lens and contexts and len(lens) == ctx.num_reqs and ctx.max_query_len * group > 16:
+        long_count = sum(1 for n in lens if n * group > 16)
+        if 0 < long_count < ctx.num_reqs and all(n * group > 16 for n in lens[:long_count]):
+            runs = [(_RequestRun(ctx, begin, end), table[begin:end])
+                    for begin, end in ((0, long_count), (long_count, ctx.num_reqs))]
+    for run, run_table in runs:
+        max_rows = run.max_query_len * group
+        split_mode = max_rows <= 16
+        alias = keys.data_ptr() == values.data_ptr() and tuple(key_strides) == tuple(value_strides) and maps == 1
+        block, slices, _ = _flash_dims_geometry(key_width, value_width, split_mode, alias)
+        splits = num_splits
+        if splits is None:
+            splits = 1
+            if run.max_query_len == 1:       # decoded tokens only: fill the GPU by cutting the keys
+                bound = getattr(run, "max_seq_len_bound", 0) or run.max_seq_len
+                tiles = 1 if split_mode else -(-max_rows // 64)
+                splits = decode_splits(run.num_reqs * tiles, value_heads * maps * slices, bound, sm_count(q.device))
+        scratch = None
+        if splits > 1:
+            tile_m, tiles = (16, 1) if split_mode else (64, -(-max_rows // 64))
+            scratch = torch.empty(run.num_reqs * value_heads * maps * slices * tiles * splits * tile_m * (block + 2),
+                                  dtype=torch.float32, device=q.device)
+        _call("kvb_flash_dims_attention", out.data_ptr(), out.stride(0), out.stride(1),
+              int(out.dtype == torch.float32), q.data_ptr(), q.stride(0), q.stride(1), keys.data_ptr(), *key_strides,
+              values.data_ptr(), *value_strides, run_table.data_ptr(), run_table.stride(0),
+              run.query_start.data_ptr(), run.context_lens.data_ptr(), None if sink is None else sink.data_ptr(),
+              run.num_reqs, run.max_query_len, value_heads, group, maps, key_width, value_width, page_size,
+              num_pages, float(scale), int(window or 0), splits, None if scratch is None else scratch.data_ptr(),
+              _stream(), kernels=2 if splits > 1 else 1)
 
 
 def latent_prepare(kv_rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, dims: int,

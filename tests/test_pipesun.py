@@ -1,0 +1,389 @@
+"""The Pipesun decoder through the framework (configuration, loader, cache manager, step function,
+scheduler, entry point) against the plain statement in tests/plain_pipesun.py, on the host with the
+stand-in kernels and on the GPU with the CUDA kernels, in 32-bit and in bfloat16.
+
+Small configurations of their own and random weights: whole prompts against token-by-token decoding,
+portions down to one and two tokens, mixed batches against each request alone, pages and state slots used
+again (freed pages overwritten), the first tokens of a request (the shift's zeros, the sink alone with one
+key), long decoding, sizes that make mechanisms coincide (one head a group, equal key and value sizes, one
+head, a turned part that is only partly turned or absent, no feed-forward, borrowed keys across other
+layers), and greedy generation through the entry point."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kernels
+import plain_pipesun as P
+import replay_cases as rc
+from kvcore_b200 import (CacheConfig, DeviceConfig, KVCoreConfig, ModelConfig, SamplingParams, SchedulerConfig)
+from kvcore_b200.config import ConfigError
+from kvcore_b200.config.registry import model_spec_from_config
+from kvcore_b200.engine.llm_engine import GenerationRequest, LLMEngine
+from kvcore_b200.weights.safetensors_io import write_safetensors
+
+BACKENDS = [pytest.param("cpu", id="host"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
+# largest |difference| of a row over the request's largest |logit|; in bfloat16 also the root mean square of a
+# row's difference (its mean taken off) over that of the request's logits
+TOLERANCE = {"float32": 3e-5, "bfloat16": 6e-2}
+# The difference of two score maps divided by its own root mean square makes these tiny models lose more in
+# bfloat16 than a plain attention does (measured with the stand-in kernels, which round where the product
+# rounds: a median row at 0.6e-2 to 1.2e-2, the worst row at 1.7e-2 to 4.6e-2), so a single row may stray to
+# 6e-2 while the median row of a trace must stay below 2e-2: a kernel that is a little wrong everywhere fails
+# the second, a wrong key or a lost state the first (and the 32-bit runs, at 3e-5).
+BF16_RMS_TOLERANCE = 6e-2
+BF16_MEDIAN_RMS_TOLERANCE = 2e-2
+
+
+@pytest.fixture(params=BACKENDS)
+def device(request, monkeypatch):
+    if request.param == "cpu":
+        plain_kernels.install(monkeypatch)
+    return request.param
+
+
+D, L = P.differential_layer, P.latent_layer
+CONFIGS = {
+    # both mixers, two heads a group, a layer that borrows the keys and values of the one in front
+    "both_mixers": P.model_config([
+        L(heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=32),
+        D(heads=4, kv_heads=2, dim=16, vdim=24),
+        D(heads=4, kv_heads=2, dim=16, vdim=24, kv_from=1, diff=0.7),
+        L(heads=2, dim=8, rot_dim=4, vdim=40, kv_rank=24, base=50.0),
+    ], vocab=96, width=32),
+    # what the first makes unequal is equal here and the other way round: one head a group, key and value
+    # sizes equal or the values smaller, one head, part of the turned part turned, no turned part, no
+    # feed-forward, keys borrowed across layers of the other kind, sizes no 16-byte vector fits
+    "coincide": P.model_config([
+        D(heads=2, kv_heads=2, dim=20, vdim=20, diff=0.05, ff=None),
+        L(heads=1, dim=8, rot_dim=12, rot_dims=4, vdim=8, kv_rank=8, ff=24),
+        L(heads=3, dim=24, rot_dim=0, vdim=10, kv_rank=18, ff=None),
+        D(heads=2, kv_heads=2, dim=20, vdim=20, diff=0.5, kv_from=0, scale=0.4),
+        D(heads=1, kv_heads=1, dim=36, vdim=12, diff=0.2),
+        D(heads=3, kv_heads=1, dim=36, vdim=12, diff=0.9, kv_from=4, ff=24),
+    ], vocab=61, width=40, eps=1e-6),
+    # sizes the tensor-core kernels take (widths in steps of 16), several pages and key tiles
+    "serving_sizes": P.model_config([
+        D(heads=4, kv_heads=1, dim=64, vdim=128),
+        L(heads=8, dim=32, rot_dim=32, vdim=32, kv_rank=96),
+        D(heads=4, kv_heads=1, dim=64, vdim=128, kv_from=0),
+        D(heads=4, kv_heads=2, dim=32, vdim=48),
+    ], vocab=128, width=64),
+}
+LENGTHS = {"both_mixers": (1, 23, 45, 70, 37, 2), "coincide": (64, 1, 30, 50), "serving_sizes": (150, 3, 97, 61)}
+
+
+def write_folder(folder, cfg, seed):
+    weights = P.random_weights(cfg, seed)
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(folder / "model.safetensors", {k: v.to(torch.bfloat16) for k, v in weights.items()})
+    return {k: v.double() for k, v in weights.items()}
+
+
+@pytest.fixture(scope="module", params=list(CONFIGS))
+def case(request, tmp_path_factory):
+    name = request.param
+    cfg = CONFIGS[name]
+    folder = tmp_path_factory.mktemp(f"pipesun_{name}")
+    weights = write_folder(folder, cfg, seed=len(name))
+    requests = {f"q{i}": rc.random_tokens(cfg["vocab"], n, 30 + i) for i, n in enumerate(LENGTHS[name])}
+    reference = {rid: P.forward(cfg, weights, toks).numpy() for rid, toks in requests.items()}
+    return dict(name=name, cfg=cfg, folder=folder, weights=weights, requests=requests, reference=reference)
+
+
+def compare(rows, reference, dtype):
+    assert rows
+    spread = []
+    for (rid, pos), row in sorted(rows.items()):
+        assert np.isfinite(row).all(), f"non-finite logits for {rid}@{pos}"
+        err = np.abs(row - reference[rid][pos]).max() / np.abs(reference[rid]).max()
+        assert err <= TOLERANCE[dtype], f"{rid}: first wrong position {pos} (error {err:.3e})"
+        if dtype == "bfloat16":
+            diff = row - reference[rid][pos]
+            rms = np.sqrt(np.mean((diff - diff.mean()) ** 2)) / reference[rid].std()
+            assert rms <= BF16_RMS_TOLERANCE, f"{rid}: first wrong position {pos} (rms error {rms:.3e})"
+            spread.append(rms)
+    if spread:
+        assert np.median(spread) <= BF16_MEDIAN_RMS_TOLERANCE, f"median rms error {np.median(spread):.3e}"
+
+
+# ---- configuration -----------------------------------------------------------------------------------
+def test_config_names_the_tensors_of_the_plain_statement():
+    from kvcore_b200.parts.model import build_model
+
+    for cfg in CONFIGS.values():
+        spec = model_spec_from_config(cfg)
+        assert spec.architecture == "Pipesun"
+        model = build_model(spec, dtype=torch.float32, device="meta")
+        shapes = {slot.name: slot.shape for slot in model.weight_slots()}
+        assert shapes == P.tensor_shapes(cfg)
+
+
+def test_config_gives_every_constant_to_the_parts():
+    cfg = CONFIGS["coincide"]
+    spec = model_spec_from_config(cfg)
+    assert [entry.cache_of for entry in spec.schedule] == [None, None, None, 0, None, 4]
+    latent = spec.layers[1].mixer.params
+    assert (latent["rot_dim"], latent["rot_dims"], latent["kv_rank"], latent["rot_base"]) == (12, 4, 8, 10000.0)
+    borrowed = spec.layers[3].mixer.params
+    assert (borrowed["own_kv"], borrowed["scale"], borrowed["diff"], borrowed["eps"]) == (False, 0.4, 0.5, 1e-6)
+    assert spec.layers[0].feed_forward is None and "feed_forward_norm" not in spec.layers[0].norms
+    assert spec.layers[5].feed_forward.params["intermediate_size"] == 24
+    assert [layer.block.params["depth"] for layer in spec.layers] == [1, 2, 3, 4, 5, 6]
+    assert {layer.block.params["depth_slots"] for layer in spec.layers} == {7}
+
+
+@pytest.mark.parametrize("change,message", [
+    (lambda c: c["layers"][0].update(type="recurrent"), "mixer of this design"),
+    (lambda c: c["layers"][0]["mlp"].update(kind="moe"), "feed-forward of this design"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "even"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=10), "at most rot_dim"),
+    (lambda c: c["layers"][1]["mixer"].update(heads=3), "multiple"),
+    (lambda c: c["layers"][2]["mixer"].update(kv_from=2), "earlier layer"),
+    (lambda c: c["layers"][2]["mixer"].update(kv_from=0), "keys and values of its own"),
+    (lambda c: c["layers"][2]["mixer"].update(vdim=8), "differs from layer 1"),
+    (lambda c: c["layers"][1]["mixer"].pop("diff"), "diff"),
+    (lambda c: c.pop("norm"), "norm"),
+])
+def test_config_refuses(change, message):
+    cfg = json.loads(json.dumps(CONFIGS["both_mixers"]))
+    change(cfg)
+    with pytest.raises(ConfigError, match=message):
+        model_spec_from_config(cfg)
+
+
+def test_cache_groups_and_state():
+    """A token's keys and values are one cached row; the two mixers are page groups of their own; a layer
+    that borrows has no pages; every layer keeps the shift's last row per request."""
+    from kvcore_b200.cache.kv_manager import group_entries
+    from kvcore_b200.parts.model import build_model
+
+    model = build_model(model_spec_from_config(CONFIGS["both_mixers"]), dtype=torch.float32, device="meta")
+    requirements = model.entry_requirements()
+    groups, entry_group = group_entries(requirements)
+    assert [(g.planes, g.heads, g.width, g.entries) for g in groups] == [
+        (1, 1, 32 + 8, (0,)), (1, 1, 2 * 2 * 16 + 2 * 24, (1,)), (1, 1, 24 + 4, (3,))]
+    assert entry_group == {0: 0, 1: 1, 2: 1, 3: 2}
+    assert all(req.block_state_spec.shape == (32,) and req.block_state_spec.dtype == torch.float32 for req in requirements)
+
+
+# ---- the cuttings ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuttings_match_the_plain_statement(case, dtype, device, tmp_path):
+    cfg, requests = case["cfg"], case["requests"]
+    traces = {
+        "whole": rc.trace_whole(requests),
+        "tail": rc.trace_decode_tail(requests, tail=20),
+        "chunks": rc.trace_chunks(requests, sizes=(7, 3, 16, 2, 5, 1, 9, 2, 31)),
+        "mixed": rc.trace_mixed(requests, max_live=4, seed=3),
+    }
+    results = {}
+    for name, steps in traces.items():
+        out = tmp_path / name
+        rc.run_inprocess(case["folder"], dtype, steps, out, rc.peak_tokens(steps), device=device,
+                         fill_freed_pages="poison" if name == "mixed" else None)
+        rows = rc.collect(steps, out, cfg["vocab"])
+        assert len(rows) == sum(len(t) for t in requests.values())
+        compare(rows, case["reference"], dtype)
+        results[name] = rows
+    if dtype == "float32" and device != "cpu":
+        # every kernel of the 32-bit path sums in an order that depends on the position only
+        for name in ("tail", "chunks", "mixed"):
+            for key, row in results["whole"].items():
+                assert np.array_equal(row, results[name][key]), f"{name} differs from whole at {key}"
+
+
+def test_residual_stream_after_every_layer(case, device):
+    """Layer by layer: the 32-bit stream that each block hands on against the plain statement's."""
+    from kvcore_b200.engine.step import StepEntry
+    from kvcore_b200.engine.trace_replay import build_replay
+
+    tokens = case["requests"]["q1"] if len(case["requests"]["q1"]) > 1 else case["requests"]["q2"]
+    step_function, kv = build_replay(str(case["folder"]), "float32", 256, device=device)
+    seen = []
+    for block in step_function.model.blocks:
+        original = block.forward
+
+        def recording(h, residual, ctx, cache, original=original):
+            out = original(h, residual, ctx, cache)
+            seen.append(out[1].detach().clone().cpu())
+            return out
+        block.forward = recording
+    assert kv.allocate_slots("x", len(tokens))
+    step_function.step([StepEntry("x", tokens, [len(tokens) - 1])])
+    collected = []
+    P.forward(case["cfg"], case["weights"], tokens, collected)
+    assert len(seen) == len(collected)
+    for index, (got, want) in enumerate(zip(seen, collected)):
+        assert got.dtype == torch.float32
+        torch.testing.assert_close(got.double(), want, rtol=2e-5, atol=2e-5, msg=lambda m: f"layer {index}: {m}")
+
+
+def test_pages_and_slots_are_used_again(case, device, tmp_path):
+    """A pool for the largest live set only: the trace needs more pages over its life than the pool has and
+    more requests than state slots in a row, so a new request finds a page and a shift row that another has
+    left (the row must read as zeros, the page must not be read before it is written)."""
+    requests = dict(case["requests"])
+    requests.update({f"again{i}": toks for i, toks in enumerate(case["requests"].values())})
+    steps = rc.trace_mixed(requests, max_live=3, seed=11)
+    peak = rc.peak_tokens(steps)
+    assert sum(-(-len(t) // 16) * 16 for t in requests.values()) > peak
+    out = tmp_path / "o"
+    step_function, kv = rc.run_inprocess(case["folder"], "float32", steps, out, peak, device=device,
+                                         fill_freed_pages="poison")
+    assert all(pool.num_free == pool.num_usable for pool in kv.pools)
+    reference = dict(case["reference"])
+    reference.update({f"again{i}": ref for i, ref in enumerate(case["reference"].values())})
+    compare(rc.collect(steps, out, case["cfg"]["vocab"]), reference, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, device, tmp_path):
+    """Two prompt tokens, then single tokens across many pages (on the GPU: decode graphs captured and replayed)."""
+    cfg = CONFIGS["serving_sizes"] if device != "cpu" else CONFIGS["both_mixers"]
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=5)
+    tokens = rc.random_tokens(cfg["vocab"], 150 if device != "cpu" else 60, 77)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:2], "want": [0, 1]}], "end": []}]
+    for pos in range(2, len(tokens)):
+        steps.append({"step": pos - 1, "entries": [{"id": "a", "tokens": [tokens[pos]], "want": [0]}],
+                      "end": ["a"] if pos == len(tokens) - 1 else []})
+    out = tmp_path / "o"
+    rc.run_inprocess(folder, dtype, steps, out, 192, device=device, fill_freed_pages="poison")
+    compare(rc.collect(steps, out, cfg["vocab"]), {"a": P.forward(cfg, weights, tokens).numpy()}, dtype)
+
+
+def test_each_mechanism_changes_the_logits():
+    """The plain statement itself: leaving a mechanism out moves the logits by far more than any tolerance
+    here, so a test that passes has seen it.  (Guards the tests, not the product.)"""
+    cfg = CONFIGS["both_mixers"]
+    weights = P.random_weights(cfg, 9, dtype=torch.float64)
+    tokens = rc.random_tokens(cfg["vocab"], 40, 3)
+    base = P.forward(cfg, weights, tokens)
+
+    def moved(config=None, **tensors):
+        other = dict(weights)
+        other.update(tensors)
+        return float((P.forward(config or cfg, other, tokens) - base).abs().max() / base.abs().max())
+
+    def changed(change):
+        other = json.loads(json.dumps(cfg))
+        change(other)
+        return other
+
+    zeros, ones = torch.zeros_like, torch.ones_like
+    assert moved(**{"l0.shift": zeros(weights["l0.shift"])}) > 1e-3                     # the token shift
+    assert moved(**{"l3.mix.sink": weights["l3.mix.sink"] - 30.0}) > 1e-3               # the sink
+    last_only = zeros(weights["l2.dwa"])
+    last_only[-1] = weights["l2.dwa"][-1]
+    assert moved(**{"l2.dwa": last_only}) > 1e-3                                          # the depth average
+    assert moved(**{"l1.mix.lq1": zeros(weights["l1.mix.lq1"])}) > 1e-3                 # lambda
+    assert moved(**{"l1.mix.k.norm": ones(weights["l1.mix.k.norm"])}) > 1e-3            # the k norm's weight
+    assert moved(**{"l0.norm1b": ones(weights["l0.norm1b"])}) > 1e-3                    # the norm behind the mixer
+    assert moved(**{"l0.mix.g": zeros(weights["l0.mix.g"])}) > 1e-3                     # the output gate
+    assert moved(changed(lambda c: c["layers"][0]["mixer"]["rot"].update(dims=4))) > 1e-3
+    assert moved(changed(lambda c: c["layers"][0]["mixer"]["rot"].update(base=77.0))) > 1e-3
+    assert moved(changed(lambda c: c["layers"][2]["mixer"].update(diff=0.1))) > 1e-3
+    own = changed(lambda c: c["layers"][2]["mixer"].pop("kv_from"))                        # borrowed keys and values
+    extra = {name: t for name, t in P.random_weights(own, 9, dtype=torch.float64).items() if name not in weights}
+    assert extra and moved(own, **extra) > 1e-3
+
+
+# ---- the entry point and the scheduler -------------------------------------------------------------------
+def plain_greedy(cfg, weights, prompt, steps):
+    tokens = list(prompt)
+    for _ in range(steps):
+        tokens.append(int(P.forward(cfg, weights, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
+
+
+@pytest.mark.parametrize("name,budget", [("both_mixers", 16), ("coincide", 7)])
+def test_greedy_generation_through_the_entry_point(device, tmp_path, name, budget):
+    cfg = CONFIGS[name]
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=21)
+    prompts = [rc.random_tokens(cfg["vocab"], n, 60 + i) for i, n in enumerate((5, 19, 33))]
+    config = KVCoreConfig(
+        model_config=ModelConfig(model=str(folder), dtype="float32", max_model_len=128),
+        cache_config=CacheConfig(block_size=16, num_gpu_blocks=24),
+        scheduler_config=SchedulerConfig(max_num_seqs=4, max_num_scheduled_tokens=budget,
+                                         max_num_partial_prefills=4, max_long_partial_prefills=4),
+        device_config=DeviceConfig(device=device),
+    )
+    engine = LLMEngine(config)
+    requests = [GenerationRequest(f"g{i}", SamplingParams(max_tokens=12, temperature=0.0), tuple(p))
+                for i, p in enumerate(prompts)]
+    outputs = engine.generate(requests)
+    for prompt, output in zip(prompts, outputs):
+        assert list(output.output_token_ids) == plain_greedy(cfg, weights, prompt, 12)
+    kv = engine.engine_core.model_runner.kv_manager
+    kv.check_invariants()
+    assert not kv.live_requests()
+
+
+def test_generation_with_few_pages_and_preemption(device, tmp_path):
+    """So few pages that a running request is preempted and computed again from its first token: its state
+    slot must read as new (the shift's zeros), not as the row it left."""
+    cfg = CONFIGS["both_mixers"]
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=22)
+    prompts = [rc.random_tokens(cfg["vocab"], n, 90 + i) for i, n in enumerate((30, 28, 26))]
+    config = KVCoreConfig(
+        model_config=ModelConfig(model=str(folder), dtype="float32", max_model_len=64),
+        cache_config=CacheConfig(block_size=16, num_gpu_blocks=7),
+        scheduler_config=SchedulerConfig(max_num_seqs=3, max_num_scheduled_tokens=32,
+                                         max_num_partial_prefills=3, max_long_partial_prefills=3),
+        device_config=DeviceConfig(device=device),
+    )
+    engine = LLMEngine(config)
+    requests = [GenerationRequest(f"g{i}", SamplingParams(max_tokens=10, temperature=0.0), tuple(p))
+                for i, p in enumerate(prompts)]
+    for prompt, output in zip(prompts, engine.generate(requests)):
+        assert list(output.output_token_ids) == plain_greedy(cfg, weights, prompt, 10)
+
+
+# ---- the programs, each in a process of its own ------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program_on_a_pipesun_folder(case, dtype, tmp_path):
+    """``bin/trace_run`` as a user drives it: a step, its ``done`` line, the next step."""
+    if case["name"] != "serving_sizes":
+        pytest.skip("one configuration is enough for the subprocess run")
+    steps = rc.trace_mixed(case["requests"], max_live=3, seed=5)
+    steps.insert(1, {"step": 1000, "entries": [], "end": []})      # a step that brings nothing
+    out = tmp_path / "out"
+    rc.run_subprocess(case["folder"], dtype, steps, out, rc.peak_tokens(steps))
+    rows = rc.collect(steps, out, case["cfg"]["vocab"])
+    assert len(rows) == sum(len(t) for t in case["requests"].values())
+    compare(rows, case["reference"], dtype)
+
+
+@pytest.mark.gpu
+def test_offline_batch_program_on_a_pipesun_folder(tmp_path):
+    import ast
+    import re
+    import subprocess
+    import sys
+
+    cfg = CONFIGS["serving_sizes"]
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=4)
+    prompts = {f"req-{i}": rc.random_tokens(cfg["vocab"], n, 80 + i) for i, n in enumerate((70, 9, 33))}
+    (tmp_path / "requests.json").write_text(json.dumps(
+        [dict(request_id=rid, prompt_token_ids=tokens) for rid, tokens in prompts.items()]))
+    command = [sys.executable, str(rc.ROOT / "bin" / "kvcore_offline_batch"), "--model", str(folder), "--dtype", "float32",
+               "--prompt-tokens-file", str(tmp_path / "requests.json"), "--max-tokens", "6", "--block-size", "16",
+               "--num-gpu-blocks", "64", "--max-model-len", "256", "--max-num-seqs", "4",
+               "--max-num-scheduled-tokens", "48", "--max-num-partial-prefills", "4", "--max-long-partial-prefills", "4",
+               "--log-level", "WARNING"]
+    result = subprocess.run(command, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr[-2000:]
+    found = {m["id"]: list(ast.literal_eval(m["ids"])) for m in re.finditer(
+        r"^\[(?P<id>[^\]]+)\] finish_reason=\S+\ntoken_ids=(?P<ids>\(.*\))$", result.stdout, re.M)}
+    assert list(found) == list(prompts)
+    for rid, prompt in prompts.items():
+        assert found[rid] == plain_greedy(cfg, weights, prompt, 6)

@@ -626,6 +626,27 @@ def toposun_config(size: dict, feed_forward: str, window: int, keep_first: int) 
             "layers": [layer] * DESIGN_LAYERS}
 
 
+def pipesun_config(size: dict, kinds: str) -> dict:
+    """A Pipesun config.json of ``DESIGN_LAYERS`` layers.  ``kinds``: a letter per layer, "d" differential
+    attention (two score maps a head: half of Llama's heads, values twice as wide, so that every projection
+    has Llama's size), "b" the same reading the keys and values of the layer in front, "l" latent attention
+    (Llama's heads, 64 turned entries, a latent of 512)."""
+    layers = []
+    for index, kind in enumerate((kinds * DESIGN_LAYERS)[:DESIGN_LAYERS]):
+        if kind == "l":
+            mixer = {"heads": size["heads"], "dim": size["dim"], "rot_dim": 64, "vdim": size["dim"], "kv_rank": 512,
+                     "rot": {"base": 10000.0, "dims": 64}, "scale": (size["dim"] + 64) ** -0.5}
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}})
+            continue
+        mixer = {"heads": size["heads"] // 2, "kv_heads": size["kv_heads"] // 2, "dim": size["dim"],
+                 "vdim": 2 * size["dim"], "scale": size["dim"] ** -0.5, "diff": 0.5}
+        if kind == "b":
+            mixer["kv_from"] = index - 1
+        layers.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}})
+    return {"architecture": "Pipesun", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
 def llama_config(size: dict) -> dict:
     return dict(LLAMA_31_8B, hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=DESIGN_LAYERS,
                 num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
@@ -670,12 +691,19 @@ def compare_designs(args) -> int:
     peaks = measured_peaks()
     for size_name in ([args.design_size] if args.design_size else list(DESIGN_SIZES)):
         size = DESIGN_SIZES[size_name]
-        models = {
-            "llama": llama_config(size),
-            "toposun_dense_full_window": toposun_config(size, "dense", 1 << 20, 0),
-            "toposun_dense": toposun_config(size, "dense", 1024, 4),
-            "toposun_moe": toposun_config(size, "moe", 1024, 4),
-        }
+        models = {"llama": llama_config(size)}
+        if args.designs_of == "toposun":
+            models.update({
+                "toposun_dense_full_window": toposun_config(size, "dense", 1 << 20, 0),
+                "toposun_dense": toposun_config(size, "dense", 1024, 4),
+                "toposun_moe": toposun_config(size, "moe", 1024, 4),
+            })
+        else:
+            models.update({
+                "pipesun_differential": pipesun_config(size, "d"),
+                "pipesun_latent": pipesun_config(size, "l"),
+                "pipesun_mixed": pipesun_config(size, "lldb"),
+            })
         for model_name, raw in models.items():
             config, runner = build_runner({}, DESIGN_LAYERS, max(batches), max_len, pages,
                                           max(PREFILL_TOKENS, max(batches)), raw_config=raw)
@@ -744,6 +772,8 @@ def main() -> int:
     parser.add_argument("--designs", action="store_true",
                         help="instead: Toposun (dense and mixture feed-forward) beside a Llama of equal layer sizes, "
                              "prefill and decode throughput and each kernel's share of a step; prints a line of its own")
+    parser.add_argument("--designs-of", default="toposun", choices=["toposun", "pipesun"],
+                        help="which design --designs sets beside Llama")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one size of --designs")
     args = parser.parse_args()
     if args.designs:

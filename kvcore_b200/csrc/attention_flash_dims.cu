@@ -467,7 +467,10 @@ static int fd_launch_shape(const FlashDimsParams& p, int max_rows, cudaStream_t 
 template <int DVB>
 static int fd_launch(const FlashDimsParams& p, bool split_mode, int max_rows, cudaStream_t stream) {
   if (split_mode) return fd_launch_shape<DVB, 64, true>(p, max_rows, stream);
-  if (p.DK > 256) return fd_launch_shape<DVB, 32, false>(p, max_rows, stream);
+  // tiles of 64 keys while two blocks of them fit a multiprocessor's shared memory, else tiles of 32
+  size_t wide = 4 * 64 * sizeof(long long) + (size_t)(64 + 2 * 64) * (p.DK + FD_PAD) * sizeof(bf16);
+  if (!p.v_in_k) wide += (size_t)2 * 64 * (DVB + FD_PAD) * sizeof(bf16);
+  if (wide > 113 * 1024) return fd_launch_shape<DVB, 32, false>(p, max_rows, stream);
   return fd_launch_shape<DVB, 64, false>(p, max_rows, stream);
 }
 

@@ -161,6 +161,7 @@ struct KvbTrace {
 #define KVB_TAG_GATE_MUL 33
 #define KVB_TAG_FLASH_DIMS 34
 #define KVB_TAG_FLASH_DIMS_COMBINE 35
+#define KVB_TAG_GATHER_CACHED 36
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

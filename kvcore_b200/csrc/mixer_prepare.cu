@@ -31,14 +31,17 @@ latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const 
                       T* __restrict__ cache, int page_size, int num_pages, int write, const T* __restrict__ q,
                       long long q_token_stride, long long q_head_stride, int q_width,
                       const T* __restrict__ q_latent, long long ql_token_stride, long long ql_head_stride,
-                      T* __restrict__ q_out, int heads, int rank, int rot, int* status) {
+                      T* __restrict__ q_out, int heads, int rank, int rot, int lead, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_LATENT_PREPARE);
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int pos = positions[t];
   const float fpos = (float)pos;
-  const int row_width = rank + rot;
-  if (write) {
+  const int row_width = rank + rot;     // of a cached row
+  const int q_row = lead + rot;         // of a row of q_out: `lead` entries the caller fills or q_latent gives, then the turned part
+  // blockIdx.y: a query head, or (the last one) the token's cached row
+  if (blockIdx.y == heads) {
+    if (!write) return;
     const T* src = kv_rows + (size_t)t * kv_stride;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < rank; i += MP_THREADS) {
@@ -66,10 +69,11 @@ latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const 
       }
       if ((rot & 1) && threadIdx.x == 0) dst[rank + rot - 1] = src[rank + rot - 1];
     }
+    return;
   }
-  // query rows: the turned position part behind the latent part
-  for (int i = threadIdx.x; i < heads * (rot / 2); i += MP_THREADS) {
-    const int h = i / (rot / 2), j = i % (rot / 2);
+  // a query row: the turned position part behind the latent part
+  const int h = blockIdx.y;
+  for (int j = threadIdx.x; j < rot / 2; j += MP_THREADS) {
     const T* src = q + (size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width;
     float u = to_float(src[2 * j]), v = to_float(src[2 * j + 1]);
     if (2 * j < dims) {
@@ -78,20 +82,28 @@ latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const 
       const float nu = u * c - v * s, nv = v * c + u * s;
       u = nu; v = nv;
     }
-    T* dst = q_out + ((size_t)t * heads + h) * row_width + rank;
+    T* dst = q_out + ((size_t)t * heads + h) * q_row + lead;
     dst[2 * j] = from_float<T>(u);
     dst[2 * j + 1] = from_float<T>(v);
   }
-  if (rot & 1)
-    for (int h = threadIdx.x; h < heads; h += MP_THREADS)
-      q_out[((size_t)t * heads + h) * row_width + rank + rot - 1] =
-          q[(size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + rot - 1];
-  if (q_latent != nullptr)
-    for (int i = threadIdx.x; i < heads * rank; i += MP_THREADS) {
-      const int h = i / rank, j = i % rank;
-      q_out[((size_t)t * heads + h) * row_width + j] =
-          q_latent[(size_t)t * ql_token_stride + (size_t)h * ql_head_stride + j];
+  if ((rot & 1) && threadIdx.x == 0)
+    q_out[((size_t)t * heads + h) * q_row + lead + rot - 1] =
+        q[(size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + rot - 1];
+  if (q_latent != nullptr) {
+    const T* src = q_latent + (size_t)t * ql_token_stride + (size_t)h * ql_head_stride;
+    T* dst = q_out + ((size_t)t * heads + h) * q_row;
+    constexpr int N = Vec16<T>::N;
+    if (lead % N == 0 && q_row % N == 0 && ql_token_stride % N == 0 && ql_head_stride % N == 0 &&
+        aligned16(q_latent) && aligned16(q_out)) {
+      for (int j = threadIdx.x * N; j < lead; j += MP_THREADS * N) {
+        Vec16<T> v;
+        v.load(src + j);
+        v.store(dst + j);
+      }
+    } else {
+      for (int j = threadIdx.x; j < lead; j += MP_THREADS) dst[j] = src[j];
     }
+  }
 }
 
 extern "C" int kvb_latent_prepare(const void* kv_rows, long long kv_stride, const void* norm_weight, float eps,
@@ -100,22 +112,80 @@ extern "C" int kvb_latent_prepare(const void* kv_rows, long long kv_stride, cons
                                   int write, const void* q, long long q_token_stride, long long q_head_stride,
                                   int q_width, const void* q_latent, long long ql_token_stride,
                                   long long ql_head_stride, void* q_out, int tokens, int heads, int rank, int rot,
-                                  int dtype, cudaStream_t stream) {
+                                  int lead, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  KVB_REQUIRE(rank > 0 && rot >= 0 && heads > 0 && dims >= 0 && dims <= rot && dims % 2 == 0,
-              "latent_prepare: bad sizes");
+  KVB_REQUIRE(rank > 0 && rot >= 0 && heads > 0 && heads < 65535 && dims >= 0 && dims <= rot && dims % 2 == 0 &&
+              lead > 0, "latent_prepare: bad sizes");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "latent_prepare: no status word");
   if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<float>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<float>), dim3(tokens, heads + 1), dim3(MP_THREADS), 0, stream, true,
         (const float*)kv_rows, kv_stride, (const float*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
         table_stride, (float*)cache, page_size, num_pages, write, (const float*)q, q_token_stride, q_head_stride,
-        q_width, (const float*)q_latent, ql_token_stride, ql_head_stride, (float*)q_out, heads, rank, rot, status));
+        q_width, (const float*)q_latent, ql_token_stride, ql_head_stride, (float*)q_out, heads, rank, rot, lead, status));
   else
-    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<bf16>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<bf16>), dim3(tokens, heads + 1), dim3(MP_THREADS), 0, stream, true,
         (const bf16*)kv_rows, kv_stride, (const bf16*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
         table_stride, (bf16*)cache, page_size, num_pages, write, (const bf16*)q, q_token_stride, q_head_stride,
-        q_width, (const bf16*)q_latent, ql_token_stride, ql_head_stride, (bf16*)q_out, heads, rank, rot, status));
+        q_width, (const bf16*)q_latent, ql_token_stride, ql_head_stride, (bf16*)q_out, heads, rank, rot, lead, status));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// Rows of a cache that keeps one row a token, brought together: entry n of the lists names a request (row of
+// the block table) and a position; columns [col0, col0 + cols) of that token's cached row go to
+// dst[n * dst_row_stride + h * dst_head_stride + 0..cols) for every h < copies.
+template <typename T>
+__global__ void __launch_bounds__(MP_THREADS)
+gather_cached_rows_kernel(T* __restrict__ dst, long long dst_row_stride, long long dst_head_stride, int copies,
+                          const T* __restrict__ cache, int row_width, int col0, int cols,
+                          const int* __restrict__ src_req, const int* __restrict__ src_pos,
+                          const int* __restrict__ table, int table_stride, int page_size, int num_pages, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GATHER_CACHED);
+  const int n = blockIdx.x;
+  const int pos = src_pos[n];
+  const int page = table[(size_t)src_req[n] * table_stride + pos / page_size];
+  if (page <= 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+    return;
+  }
+  const T* src = cache + ((size_t)page * page_size + pos % page_size) * row_width + col0;
+  T* out = dst + (size_t)n * dst_row_stride;
+  constexpr int N = Vec16<T>::N;
+  const bool vec = cols % N == 0 && col0 % N == 0 && row_width % N == 0 && dst_row_stride % N == 0 &&
+                   dst_head_stride % N == 0 && aligned16(cache) && aligned16(dst);
+  if (vec) {
+    const int chunks = cols / N;
+    for (int i = threadIdx.x; i < copies * chunks; i += MP_THREADS) {
+      const int h = i / chunks, c = (i % chunks) * N;
+      Vec16<T> v;
+      v.load(src + c);
+      v.store(out + (size_t)h * dst_head_stride + c);
+    }
+  } else {
+    for (int i = threadIdx.x; i < copies * cols; i += MP_THREADS) {
+      const int h = i / cols, c = i % cols;
+      out[(size_t)h * dst_head_stride + c] = src[c];
+    }
+  }
+}
+
+extern "C" int kvb_gather_cached_rows(void* dst, long long dst_row_stride, long long dst_head_stride, int copies,
+                                      const void* cache, int row_width, int col0, int cols, const int* src_req,
+                                      const int* src_pos, int count, const int* table, int table_stride,
+                                      int page_size, int num_pages, int dtype, cudaStream_t stream) {
+  if (count == 0) return 0;
+  KVB_REQUIRE(copies > 0 && cols > 0 && col0 >= 0 && col0 + cols <= row_width, "gather_cached_rows: bad columns");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "gather_cached_rows: no status word");
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((gather_cached_rows_kernel<float>), dim3(count), dim3(MP_THREADS), 0, stream, true,
+        (float*)dst, dst_row_stride, dst_head_stride, copies, (const float*)cache, row_width, col0, cols, src_req,
+        src_pos, table, table_stride, page_size, num_pages, status));
+  else
+    KVB_CHECK_CUDA(kvb_launch((gather_cached_rows_kernel<bf16>), dim3(count), dim3(MP_THREADS), 0, stream, true,
+        (bf16*)dst, dst_row_stride, dst_head_stride, copies, (const bf16*)cache, row_width, col0, cols, src_req,
+        src_pos, table, table_stride, page_size, num_pages, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
@@ -135,13 +205,14 @@ head_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const T* _
     const int pos = positions[t];
     const int page = table[(size_t)req_index[t] * table_stride + pos / page_size];
     if (page <= 0 || page >= num_pages) {
-      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
     } else {
       dst = cache + ((size_t)page * page_size + pos % page_size) * ((size_t)k_vectors * dim + v_width);
     }
   }
   const int vectors = q_vectors + (write ? k_vectors : 0);
-  for (int n = warp; n < vectors; n += MP_THREADS / 32) {
+  // blockIdx.y: a group of four vectors (one a warp); the block of the first group also copies the values
+  for (int n = blockIdx.y * (MP_THREADS / 32) + warp; n < vectors; n = vectors) {
     const bool is_q = n < q_vectors;
     T* vec = row + (size_t)n * dim;
     const T* w = is_q ? q_weight : k_weight;
@@ -155,7 +226,7 @@ head_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const T* _
     if (o != nullptr)
       for (int i = lane; i < dim; i += 32) o[i] = from_float<T>(to_float(vec[i]) * inv * to_float(w[i]));
   }
-  if (dst != nullptr) {
+  if (dst != nullptr && blockIdx.y == 0) {
     const T* v = row + (size_t)(q_vectors + k_vectors) * dim;
     for (int i = threadIdx.x; i < v_width; i += MP_THREADS) dst[(size_t)k_vectors * dim + i] = v[i];
   }
@@ -170,12 +241,14 @@ extern "C" int kvb_head_norm_kv_write(void* rows, long long row_stride, const vo
   KVB_REQUIRE(q_vectors > 0 && k_vectors > 0 && dim > 0 && v_width > 0, "head_norm_kv_write: bad sizes");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "head_norm_kv_write: no status word");
+  const int groups = (q_vectors + (write ? k_vectors : 0) + MP_THREADS / 32 - 1) / (MP_THREADS / 32);
+  KVB_REQUIRE(groups <= 65535, "head_norm_kv_write: too many vectors a token");
   if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<float>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<float>), dim3(tokens, groups), dim3(MP_THREADS), 0, stream, true,
         (float*)rows, row_stride, (const float*)q_weight, (const float*)k_weight, eps, positions, req_index, table,
         table_stride, (float*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
   else
-    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<bf16>), dim3(tokens), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<bf16>), dim3(tokens, groups), dim3(MP_THREADS), 0, stream, true,
         (bf16*)rows, row_stride, (const bf16*)q_weight, (const bf16*)k_weight, eps, positions, req_index, table,
         table_stride, (bf16*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
   KVB_CHECK_LAUNCH();

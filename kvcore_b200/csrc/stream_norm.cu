@@ -33,7 +33,12 @@ __device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (
   c = warp_sum(lane < nwarps ? scratch[2][lane] : 0.0f);
 }
 
-template <typename IN, typename OUT, typename W>
+// Rows of up to SN_THREADS * SN_KEEP entries are held in registers between the pass that sums the
+// squares and the pass that scales and stores: every load of a pass is in flight at once (a small batch is
+// bound by the latency of its loads, not by bytes).  Wider rows are read again.
+#define SN_KEEP 16
+
+template <typename IN, typename OUT, typename W, bool KEPT>
 __global__ void __launch_bounds__(SN_THREADS)
 rms_norm_shift_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* __restrict__ weight,
                       const W* __restrict__ shift, float* __restrict__ state, const int* __restrict__ req_index,
@@ -58,6 +63,46 @@ rms_norm_shift_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* 
   const IN* prow = shifting && !first ? row - width : nullptr;
   const IN* lrow = first && last != t ? x + (size_t)last * width : nullptr;
   float ss = 0.0f, sp = 0.0f, sl = 0.0f;
+  if (KEPT) {
+    float mine[SN_KEEP], before[SN_KEEP], final_row[SN_KEEP], w[SN_KEEP], mix[SN_KEEP];
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) {
+      const int i = threadIdx.x + s * SN_THREADS;
+      const bool in = i < width;
+      mine[s] = in ? to_float(row[i]) : 0.0f;
+      w[s] = in ? to_float(weight[i]) : 0.0f;
+      before[s] = 0.0f; final_row[s] = 0.0f; mix[s] = 0.0f;
+      if (shifting && in) {
+        mix[s] = to_float(shift[i]);
+        before[s] = first ? srow[i] : to_float(prow[i]);
+        if (lrow != nullptr) final_row[s] = to_float(lrow[i]);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) {
+      ss = fmaf(mine[s], mine[s], ss);
+      if (prow != nullptr) sp = fmaf(before[s], before[s], sp);
+      sl = fmaf(final_row[s], final_row[s], sl);
+    }
+    block_sum3(ss, sp, sl, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    const float inv_p = 1.0f / sqrtf(sp / (float)width + eps);
+    const float inv_l = 1.0f / sqrtf(sl / (float)width + eps);
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) {
+      const int i = threadIdx.x + s * SN_THREADS;
+      if (i >= width) continue;
+      const float y = mine[s] * inv * w[s];
+      float result = y;
+      if (shifting) {
+        const float in_front = first ? before[s] : before[s] * inv_p * w[s];
+        result = y + (in_front - y) * mix[s];
+        if (first) srow[i] = lrow != nullptr ? final_row[s] * inv_l * w[s] : y;
+      }
+      orow[i] = from_float<OUT>(result);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += SN_THREADS) {
     const float v = to_float(row[i]);
     ss = fmaf(v, v, ss);
@@ -85,8 +130,13 @@ template <typename IN, typename OUT, typename W>
 static cudaError_t launch_rms_norm_shift(void* out, const void* x, const void* w, const void* shift, float* state,
                                          const int* req_index, const int* query_start, const int* slots, int rows,
                                          int width, float eps, cudaStream_t stream) {
-  return kvb_launch((rms_norm_shift_kernel<IN, OUT, W>), dim3(rows), dim3(SN_THREADS), 0, stream, true, (OUT*)out,
-                    (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots, width, eps);
+  if (width <= SN_THREADS * SN_KEEP)
+    return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, true>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
+                      (OUT*)out, (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots,
+                      width, eps);
+  return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, false>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
+                    (OUT*)out, (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots,
+                    width, eps);
 }
 
 extern "C" int kvb_rms_norm_shift(void* out, const void* x, const void* weight, const void* shift, float* state,
@@ -120,7 +170,7 @@ extern "C" int kvb_rms_norm_shift(void* out, const void* x, const void* weight, 
   return 0;
 }
 
-template <typename T, typename W>
+template <typename T, typename W, bool KEPT>
 __global__ void __launch_bounds__(SN_THREADS)
 stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
                        const W* __restrict__ weight, int width, float eps, float* __restrict__ avg,
@@ -131,6 +181,47 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
   const size_t base = (size_t)blockIdx.x * width;
   const T* arow = a + base;
   float ss = 0.0f;
+  if (KEPT) {
+    float mine[SN_KEEP], stream[SN_KEEP], w[SN_KEEP];
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) {
+      const int i = threadIdx.x + s * SN_THREADS;
+      const bool in = i < width;
+      mine[s] = in ? to_float(arow[i]) : 0.0f;
+      stream[s] = in ? x[base + i] : 0.0f;
+      w[s] = in ? to_float(weight[i]) : 0.0f;
+      ss = fmaf(mine[s], mine[s], ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) stream[s] = stream[s] + mine[s] * inv * w[s];
+    if (avg != nullptr) {
+      // the average in ascending order of the results; the loads of one result are in flight together
+#pragma unroll
+      for (int s = 0; s < SN_KEEP; ++s) mine[s] = 0.0f;
+      for (int j = 0; j < count; ++j) {
+        const float c = to_float(coeffs[j]);
+        const float* result = stack + (size_t)j * stack_stride + base;
+#pragma unroll
+        for (int s = 0; s < SN_KEEP; ++s) {
+          const int i = threadIdx.x + s * SN_THREADS;
+          if (i < width) mine[s] = fmaf(c, result[i], mine[s]);
+        }
+      }
+      const float c = to_float(coeffs[count]);
+#pragma unroll
+      for (int s = 0; s < SN_KEEP; ++s) {
+        const int i = threadIdx.x + s * SN_THREADS;
+        if (i < width) avg[base + i] = fmaf(c, stream[s], mine[s]);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < SN_KEEP; ++s) {
+      const int i = threadIdx.x + s * SN_THREADS;
+      if (i < width) out[base + i] = stream[s];
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += SN_THREADS) {
     const float v = to_float(arow[i]);
     ss = fmaf(v, v, ss);
@@ -156,7 +247,10 @@ extern "C" int kvb_stream_add_norm(float* out, const float* x, const void* a, co
               "stream_add_norm: the depth average needs its coefficients and the results in front");
   cudaError_t err;
 #define KVB_AN_LAUNCH(T, W)                                                                                       \
-  err = kvb_launch((stream_add_norm_kernel<T, W>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,        \
+  err = width <= SN_THREADS * SN_KEEP                                                                             \
+      ? kvb_launch((stream_add_norm_kernel<T, W, true>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,  \
+                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)  \
+      : kvb_launch((stream_add_norm_kernel<T, W, false>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x, \
                    (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)
   if (dtype == KVB_F32 && weight_dtype == KVB_F32) KVB_AN_LAUNCH(float, float);
   else if (dtype == KVB_F32) KVB_AN_LAUNCH(float, bf16);

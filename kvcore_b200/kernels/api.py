@@ -78,7 +78,9 @@ def ensure_built(verbose: bool = False) -> str:
                                      _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _int,
                                      _float, _int, _int, _vp, _vp],
         "kvb_latent_prepare": [_vp, _ll, _vp, _float, _vp, _int, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _vp,
-                               _ll, _ll, _int, _vp, _ll, _ll, _vp, _int, _int, _int, _int, _int, _vp],
+                               _ll, _ll, _int, _vp, _ll, _ll, _vp, _int, _int, _int, _int, _int, _int, _vp],
+        "kvb_gather_cached_rows": [_vp, _ll, _ll, _int, _vp, _int, _int, _int, _vp, _vp, _int, _vp, _int, _int,
+                                   _int, _int, _vp],
         "kvb_head_norm_kv_write": [_vp, _ll, _vp, _vp, _float, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _int,
                                    _int, _int, _int, _int, _int, _vp],
         "kvb_maps_combine": [_vp, _vp, _ll, _int, _float, _float, _float, _int, _vp],
@@ -587,6 +589,7 @@ class _RequestRun:
         self.max_seq_len_bound = 0
         self.query_start = ctx.query_start[begin : end + 1]
         self.context_lens = ctx.context_lens[begin:end]
+        self.host_query_lens, self.host_context_lens = lens, contexts
 
 
 def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_splits, use_tma, use_tc5,
@@ -655,7 +658,7 @@ _stream_scratch: dict[int, torch.Tensor] = {}
 
 TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_rows", 30: "latent_prepare",
               31: "head_norm_kv_write", 32: "maps_combine", 33: "sigmoid_gate_mul", 34: "flash_dims",
-              35: "flash_dims_combine", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+              35: "flash_dims_combine", 36: "gather_cached_rows", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
@@ -1070,11 +1073,15 @@ def _flash_dims_geometry(key_width: int, value_width: int, split_mode: bool, val
     if block is None:
         return None
     values_in_keys = values_in_keys and slices * block <= key_width
-    keys_per_tile = 64 if split_mode or key_width <= 256 else 32
     tile_m = 16 if split_mode else 64
-    smem = 4 * keys_per_tile * 8 + (tile_m + 2 * keys_per_tile) * (key_width + 8) * 2
-    if not values_in_keys:
-        smem += 2 * keys_per_tile * (block + 8) * 2
+
+    def tiles_bytes(keys_per_tile: int) -> int:
+        total = 4 * keys_per_tile * 8 + (tile_m + 2 * keys_per_tile) * (key_width + 8) * 2
+        return total if values_in_keys else total + 2 * keys_per_tile * (block + 8) * 2
+
+    # prompts: tiles of 64 keys while two blocks of them fit a multiprocessor's shared memory, else of 32
+    keys_per_tile = 64 if split_mode or tiles_bytes(64) <= 113 * 1024 else 32
+    smem = tiles_bytes(keys_per_tile)
     if split_mode:
         smem = max(smem, 4 * keys_per_tile * 8 + tile_m * (key_width + 8) * 2 + (4 * 16 * block + 128) * 4)
     return (block, slices, smem) if smem <= 227 * 1024 else None
@@ -1144,19 +1151,26 @@ def latent_prepare(kv_rows: torch.Tensor, norm_weight: torch.Tensor, eps: float,
     first ``dims`` of the last ``rot`` are turned by the token's position (entry 2i with 2i+1, angle
     ``position * inv_freq[i]``); the row goes into the token's place of ``cache [pages, 1, page, rank + rot]``
     if ``write``.  ``q [T, H, q_width + rot]`` (a view): its last ``rot`` entries, turned the same way, go
-    behind the first ``rank`` entries of ``q_out [T, H, rank + rot]``; those first entries are copied from
-    ``q_latent [T, H, rank]`` (a view) when given."""
+    behind the first ``lead`` entries of ``q_out [T, H, lead + rot]``; those first entries are copied from
+    ``q_latent [T, H, lead]`` (a view) when given.  ``lead`` is ``rank`` when the attention runs in the latent
+    space (``q_latent``: the query carried there), or ``q_width`` when it runs on keys of ``q_width + rot``
+    entries (``q_latent``: the unturned part of ``q`` itself)."""
     _check(kv_rows, "kv_rows", contiguous=False)
     _check(q, "q", dtype=kv_rows.dtype, contiguous=False)
     _check(q_out, "q_out", dtype=kv_rows.dtype)
     _check(cache, "cache", dtype=kv_rows.dtype)
     _check(norm_weight, "norm_weight", dtype=kv_rows.dtype)
+    if ctx.positions.numel() != q_out.shape[0]:
+        raise KernelError(f"latent_prepare: {ctx.positions.numel()} positions for {q_out.shape[0]} tokens")
     _check(inv_freq, "inv_freq", dtype=torch.float32)
-    tokens, heads, row = q_out.shape
+    tokens, heads, q_row = q_out.shape
     rank = norm_weight.numel()
-    rot = row - rank
     num_pages, one, page_size, width = cache.shape
-    if (one, width) != (1, row) or tuple(kv_rows.shape) != (tokens, row) or tuple(q.shape) != (tokens, heads, q_width + rot):
+    rot = width - rank
+    lead = q_row - rot
+    row = width
+    if (one != 1 or lead not in (rank, q_width) or tuple(kv_rows.shape) != (tokens, row)
+            or tuple(q.shape) != (tokens, heads, q_width + rot)):
         raise KernelError(f"latent_prepare: shapes kv_rows {tuple(kv_rows.shape)}, q {tuple(q.shape)}, q_out "
                           f"{tuple(q_out.shape)}, cache {tuple(cache.shape)} do not fit")
     if kv_rows.stride(1) != 1 or q.stride(2) != 1 or inv_freq.numel() * 2 < dims:
@@ -1164,13 +1178,33 @@ def latent_prepare(kv_rows: torch.Tensor, norm_weight: torch.Tensor, eps: float,
     latent = (None, 0, 0)
     if q_latent is not None:
         _check(q_latent, "q_latent", dtype=kv_rows.dtype, contiguous=False)
-        if tuple(q_latent.shape) != (tokens, heads, rank) or q_latent.stride(2) != 1:
+        if tuple(q_latent.shape) != (tokens, heads, lead) or q_latent.stride(2) != 1:
             raise KernelError(f"latent_prepare: q_latent {tuple(q_latent.shape)} does not fit")
         latent = (q_latent.data_ptr(), q_latent.stride(0), q_latent.stride(1))
     _call("kvb_latent_prepare", kv_rows.data_ptr(), kv_rows.stride(0), norm_weight.data_ptr(), float(eps),
           inv_freq.data_ptr(), int(dims), ctx.positions.data_ptr(), ctx.req_index.data_ptr(), table.data_ptr(),
           table.stride(0), cache.data_ptr(), page_size, num_pages, int(write), q.data_ptr(), q.stride(0), q.stride(1),
-          int(q_width), *latent, q_out.data_ptr(), tokens, heads, rank, rot, _dtype_code(kv_rows), _stream())
+          int(q_width), *latent, q_out.data_ptr(), tokens, heads, rank, rot, lead, _dtype_code(kv_rows), _stream())
+
+
+def gather_cached_rows(cache: torch.Tensor, table: torch.Tensor, src_req: torch.Tensor, src_pos: torch.Tensor,
+                       col0: int, cols: int, out: torch.Tensor, *, copies: int = 1, head_stride: int = 0) -> None:
+    """Columns ``[col0, col0 + cols)`` of the cached rows of the tokens ``(src_req[n], src_pos[n])`` (request row
+    of ``table``, position) of ``cache [pages, 1, page, width]`` into ``out``: row ``n`` of ``out`` (a 2-D view,
+    last stride 1) gets them at its start, and again every ``head_stride`` entries, ``copies`` times."""
+    _check(cache, "cache")
+    _check(out, "out", dtype=cache.dtype, contiguous=False)
+    _check(src_req, "src_req", dtype=torch.int32)
+    _check(src_pos, "src_pos", dtype=torch.int32)
+    num_pages, one, page_size, width = cache.shape
+    count = src_req.numel()
+    if one != 1 or out.dim() != 2 or out.stride(1) != 1 or out.shape[0] < count or src_pos.numel() != count:
+        raise KernelError(f"gather_cached_rows: cache {tuple(cache.shape)} / out {tuple(out.shape)} do not fit")
+    if (copies - 1) * head_stride + cols > out.shape[1]:
+        raise KernelError("gather_cached_rows: the copies do not fit a row of out")
+    _call("kvb_gather_cached_rows", out.data_ptr(), out.stride(0), int(head_stride), int(copies), cache.data_ptr(),
+          width, int(col0), int(cols), src_req.data_ptr(), src_pos.data_ptr(), count, table.data_ptr(),
+          table.stride(0), page_size, num_pages, _dtype_code(cache), _stream())
 
 
 def head_norm_kv_write(rows: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor | None, eps: float, ctx,

@@ -16,6 +16,13 @@ cached.  The scores are taken in the latent space: ``q_h . (W_uk[h] c) = (W_uk[h
 attention runs with one key head of ``kv_rank + rot_dim`` entries whose first ``kv_rank`` entries are also
 the values, and ``W_uv[h]`` is applied to the attention's output.  The softmax has a learned sink per head;
 the heads' outputs are gated by ``sigmoid(W_g x)`` before the output projection.
+
+Long portions of prompts (bfloat16, at least ``LatentAttention.expand_min_tokens`` tokens) take the other
+reading of the same product: the latents of the request's whole context are fetched from the cache and
+carried up to per-head keys ``[W_uk[h] c | turned part]`` and values ``W_uv[h] c`` by one matrix product, and
+the attention runs on those.  A (query, key) pair then costs ``head_dim + rot_dim + value_dim``
+multiply-adds a head instead of ``2 kv_rank + rot_dim``; carrying a key up costs
+``kv_rank (head_dim + rot_dim + value_dim)`` a head once, which a portion of that many tokens repays.
 """
 from __future__ import annotations
 
@@ -23,6 +30,14 @@ import torch
 
 from .. import kernels as K
 from .base import MIXERS, CacheSpec, Mixer, WeightSlot
+
+
+class _TokenRange:
+    """Tokens ``[begin, end)`` of a step, as the kernels that work token by token need them described."""
+
+    def __init__(self, ctx, begin: int, end: int) -> None:
+        self.positions = ctx.positions[begin:end]
+        self.req_index = ctx.req_index[begin:end]
 
 
 class DifferentialAttention(Mixer):
@@ -111,7 +126,8 @@ class DifferentialAttention(Mixer):
 
 
 class LatentAttention(Mixer):
-    graph_safe = True
+    graph_safe = True     # decode steps launch by the batch's shape alone; only prompt portions plan on the host
+    expand_min_tokens = 128
 
     DEFAULT_TENSOR_NAMES = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "sink": "sink",
                             "g": "g", "o": "o"}
@@ -142,6 +158,9 @@ class LatentAttention(Mixer):
         # W_uk as [heads, kv_rank, head_dim]: the matrix that carries a head's query into the latent space
         self.uk_t = torch.empty(heads, self.kv_rank, self.head_dim, dtype=dtype, device=device)
         self.uv = torch.empty(heads, self.value_dim, self.kv_rank, dtype=dtype, device=device)
+        # rows [head_dim of W_uk[h] | rot_dim of zeros | value_dim of W_uv[h]] per head: carries latents up to
+        # per-head key/value rows in one product (made from the two tensors once the weights are there)
+        self.up_weight = None
         self.sink = torch.empty(heads, dtype=dtype, device=device) if sink else None
         self.sink_f32 = None
         self.o_weight = torch.empty(self.hidden_size, heads * self.value_dim, dtype=dtype, device=device)
@@ -174,6 +193,66 @@ class LatentAttention(Mixer):
     def finalize_weights(self) -> None:
         if self.sink is not None:
             self.sink_f32 = self.sink.to(torch.float32)
+        if self.uk_t.device.type == "cuda" and self.dtype == torch.bfloat16:
+            heads, d, r, v = self.num_heads, self.head_dim, self.rot_dim, self.value_dim
+            up = torch.zeros(heads, d + r + v, self.kv_rank, dtype=self.dtype, device=self.uk_t.device)
+            up[:, :d] = self.uk_t.transpose(1, 2)
+            up[:, d + r:] = self.uv
+            self.up_weight = up.view(heads * (d + r + v), self.kv_rank)
+
+    def _long_requests(self, ctx, rows: torch.Tensor) -> int:
+        """How many of the step's requests (they stand longest portion first) take the carried-up reading."""
+        lens = getattr(ctx, "host_query_lens", None)
+        if self.up_weight is None or rows.dtype != torch.bfloat16 or not lens or len(lens) != ctx.num_reqs:
+            return 0
+        d, r, v, width = self.head_dim, self.rot_dim, self.value_dim, self.kv_cols
+        geometry = K.api._flash_dims_geometry
+        if ((d + r) % 16 or (d + r + v) % 8 or v % 8 or geometry(d + r, v, False, False) is None
+                or width % 16 or self.kv_rank % 8 or geometry(width, self.kv_rank, False, True) is None
+                or geometry(width, self.kv_rank, True, True) is None or rows.stride(0) % 8 or self.q_cols % 8):
+            return 0
+        count = 0
+        while count < len(lens) and lens[count] >= self.expand_min_tokens:
+            count += 1
+        return count
+
+    def _attend_carried_up(self, queries, ctx, table, plane, count: int, out: torch.Tensor) -> None:
+        """The first ``count`` requests of the step on per-head keys and values made from their cached latents
+        (``queries [tokens, heads, head_dim + rot_dim]``, turned already); fills their tokens' rows of
+        ``out [T, heads, value_dim]``."""
+        heads, d, r, v, rank = self.num_heads, self.head_dim, self.rot_dim, self.value_dim, self.kv_rank
+        tokens, q = queries.shape[0], queries
+
+        def plan():
+            # per step, shared by the model's latent layers: which cached rows to fetch, and a table that
+            # addresses the fetched rows as pages of one token (row 0 stands for the null page)
+            totals = [c + n for c, n in zip(ctx.host_context_lens[:count], ctx.host_query_lens[:count])]
+            longest, rows_needed = max(totals), sum(totals)
+            req = torch.repeat_interleave(torch.arange(count, dtype=torch.int32), torch.tensor(totals))
+            pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in totals])
+            row_table = torch.zeros((count, longest), dtype=torch.int32)
+            begin = 1
+            for index, n in enumerate(totals):
+                row_table[index, :n] = torch.arange(begin, begin + n, dtype=torch.int32)
+                begin += n
+            packed = torch.cat([req, pos, row_table.view(-1)]).to(q.device, non_blocking=True)
+            return (packed[:rows_needed], packed[rows_needed:2 * rows_needed],
+                    packed[2 * rows_needed:].view(count, longest), rows_needed)
+
+        src_req, src_pos, row_table, rows_needed = ctx.shared(("carried_up_rows", count), plan)
+        latents = torch.empty((rows_needed + 1, rank), dtype=q.dtype, device=q.device)
+        latents[0].zero_()
+        K.gather_cached_rows(plane, table, src_req, src_pos, 0, rank, latents[1:])
+        per_head = d + r + v
+        carried = K.linear(latents, self.up_weight)                       # [rows + 1, heads * (d + r + v)]
+        if r:
+            K.gather_cached_rows(plane, table, src_req, src_pos, rank, r, carried[1:, d:], copies=heads,
+                                 head_stride=per_head)
+        strides = (heads * per_head, per_head, 0)
+        K.attention_dims(queries, carried, carried.view(-1)[d + r:], row_table, K.api._RequestRun(ctx, 0, count),
+                         value_heads=heads, group=1, maps=1, key_width=d + r, value_width=v, page_size=1,
+                         num_pages=rows_needed + 1, key_strides=strides, value_strides=strides, scale=self.scale,
+                         sink=self.sink_f32, out=out[:tokens])
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         if self.sink is not None and self.sink_f32 is None:
@@ -185,20 +264,44 @@ class LatentAttention(Mixer):
         table = ctx.block_table(cache.group)
         plane = cache.planes[0]                                # [pages, 1, page, kv_rank + rot_dim]
         num_pages, _, page, width = plane.shape
+        long_count = self._long_requests(ctx, rows)
+        first = sum(ctx.host_query_lens[:long_count]) if long_count else 0      # tokens of the long portions
         # the attention's queries: the head's query carried into the latent space, then its turned part
         latent_q = torch.empty((tokens, heads, width), dtype=rows.dtype, device=rows.device)
         carried = None
         if rows.dtype == torch.float32:
             K.heads_linear(q[:, :, : self.head_dim], self.uk_t, out=latent_q[:, :, :rank])
-        else:
-            carried = K.heads_linear(q[:, :, : self.head_dim], self.uk_t)
-        K.latent_prepare(kv_rows, self.kv_norm_weight, self.eps, self.inv_freq, self.rot_dims, ctx, table, plane,
-                         q, self.head_dim, latent_q, q_latent=carried, write=cache.owner)
+        elif first < tokens:
+            carried = K.heads_linear(q[first:, :, : self.head_dim], self.uk_t)
+        # every token's latent row goes into the cache here; the long portions' queries stay heads of their
+        # own: the unturned part as projected, then the turned part
+        rest = ctx if not first else _TokenRange(ctx, first, tokens)
+        queries = None
+        if first:
+            queries = torch.empty((first, heads, self.head_dim + self.rot_dim), dtype=rows.dtype, device=rows.device)
+            K.latent_prepare(kv_rows[:first], self.kv_norm_weight, self.eps, self.inv_freq, self.rot_dims,
+                             _TokenRange(ctx, 0, first), table, plane, q[:first], self.head_dim, queries,
+                             q_latent=q[:first, :, : self.head_dim], write=cache.owner)
+        if first < tokens:
+            K.latent_prepare(kv_rows[first:], self.kv_norm_weight, self.eps, self.inv_freq, self.rot_dims, rest,
+                             table, plane, q[first:], self.head_dim, latent_q[first:], q_latent=carried,
+                             write=cache.owner)
         strides = (page * width, 0, width)
-        mixed = K.attention_dims(latent_q, plane, plane, table, ctx, value_heads=1, group=heads, maps=1,
-                                 key_width=width, value_width=rank, page_size=page, num_pages=num_pages,
-                                 key_strides=strides, value_strides=strides, scale=self.scale, sink=self.sink_f32)
-        out = K.heads_linear(mixed, self.uv)                   # [T, heads, value_dim]
+        if not first:
+            mixed = K.attention_dims(latent_q, plane, plane, table, ctx, value_heads=1, group=heads, maps=1,
+                                     key_width=width, value_width=rank, page_size=page, num_pages=num_pages,
+                                     key_strides=strides, value_strides=strides, scale=self.scale, sink=self.sink_f32)
+            out = K.heads_linear(mixed, self.uv)                   # [T, heads, value_dim]
+        else:
+            out = torch.empty((tokens, heads, self.value_dim), dtype=rows.dtype, device=rows.device)
+            self._attend_carried_up(queries, ctx, table, plane, long_count, out)
+            if first < tokens:
+                mixed = torch.empty((tokens, heads, rank), dtype=rows.dtype, device=rows.device)
+                K.attention_dims(latent_q, plane, plane, table[long_count:], K.api._RequestRun(ctx, long_count, ctx.num_reqs),
+                                 value_heads=1, group=heads, maps=1, key_width=width, value_width=rank, page_size=page,
+                                 num_pages=num_pages, key_strides=strides, value_strides=strides, scale=self.scale,
+                                 sink=self.sink_f32, out=mixed)
+                K.heads_linear(mixed[first:], self.uv, out=out[first:])
         if self.g_cols:
             out = K.sigmoid_gate_mul(out, rows[:, self.q_cols + self.kv_cols :])
         else:

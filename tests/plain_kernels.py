@@ -246,9 +246,10 @@ def attention_dims(q, keys, values, table, ctx, *, value_heads, group, maps, key
 
 def latent_prepare(kv_rows, norm_weight, eps, inv_freq, dims, ctx, table, cache, q, q_width, q_out, *,
                    q_latent=None, write=True):
-    tokens, heads, row = q_out.shape
+    tokens, heads, q_row = q_out.shape
     rank = norm_weight.numel()
-    rot = row - rank
+    rot = cache.shape[3] - rank
+    lead = q_row - rot                   # the entries of a q_out row in front of the turned part
     page_size = cache.shape[2]
 
     def turn(x, pos):          # [..., rot] float, interleaved pairs of the first ``dims`` entries
@@ -268,9 +269,19 @@ def latent_prepare(kv_rows, norm_weight, eps, inv_freq, dims, ctx, table, cache,
             latent = _rms(kv_rows[t, :rank], eps) * norm_weight.float()
             cache[page, 0, pos % page_size, :rank] = latent.to(cache.dtype)
             cache[page, 0, pos % page_size, rank:] = turn(kv_rows[t, rank:].float(), pos).to(cache.dtype)
-        q_out[t, :, rank:] = turn(q[t, :, q_width:].float(), pos).to(q_out.dtype)
+        q_out[t, :, lead:] = turn(q[t, :, q_width:].float(), pos).to(q_out.dtype)
         if q_latent is not None:
-            q_out[t, :, :rank] = q_latent[t]
+            q_out[t, :, :lead] = q_latent[t]
+
+
+def gather_cached_rows(cache, table, src_req, src_pos, col0, cols, out, *, copies=1, head_stride=0):
+    page_size = cache.shape[2]
+    for n in range(src_req.numel()):
+        pos = int(src_pos[n])
+        page = int(table[int(src_req[n]), pos // page_size])
+        assert page > 0
+        for h in range(copies):
+            out[n, h * head_stride:h * head_stride + cols] = cache[page, 0, pos % page_size, col0:col0 + cols]
 
 
 def head_norm_kv_write(rows, q_weight, k_weight, eps, ctx, table, cache, *, q_vectors, k_vectors, dim, value_width,
@@ -485,7 +496,7 @@ _NAMES = [
     "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "feed_tokens", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
     "rms_norm_shift", "stream_add_norm", "attention_dims", "latent_prepare", "head_norm_kv_write", "maps_combine",
-    "sigmoid_gate_mul", "heads_linear",
+    "sigmoid_gate_mul", "heads_linear", "gather_cached_rows",
     "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
 ]
 

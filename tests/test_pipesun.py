@@ -197,6 +197,24 @@ def test_cuttings_match_the_plain_statement(case, dtype, device, tmp_path):
                 assert np.array_equal(row, results[name][key]), f"{name} differs from whole at {key}"
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("minimum", [2, 40])
+def test_long_portions_on_carried_up_keys(case, minimum, tmp_path, monkeypatch):
+    """bfloat16 on the GPU: portions of at least ``minimum`` tokens read a latent cache the other way (per-head
+    keys and values made from the cached latents of the whole context); shorter ones and decoded tokens beside
+    them in the same step stay in the latent space.  Same logits either way, within bfloat16."""
+    from kvcore_b200.parts.attention_maps import LatentAttention
+
+    monkeypatch.setattr(LatentAttention, "expand_min_tokens", minimum)
+    cfg, requests = case["cfg"], case["requests"]
+    for name, steps in (("chunks", rc.trace_chunks(requests, sizes=(7, 3, 16, 2, 5, 1, 9, 2, 61))),
+                        ("mixed", rc.trace_mixed(requests, max_live=4, seed=7))):
+        out = tmp_path / name
+        rc.run_inprocess(case["folder"], "bfloat16", steps, out, rc.peak_tokens(steps), device="cuda:0",
+                         fill_freed_pages="poison")
+        compare(rc.collect(steps, out, cfg["vocab"]), case["reference"], "bfloat16")
+
+
 def test_residual_stream_after_every_layer(case, device):
     """Layer by layer: the 32-bit stream that each block hands on against the plain statement's."""
     from kvcore_b200.engine.step import StepEntry

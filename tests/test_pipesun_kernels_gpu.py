@@ -136,6 +136,46 @@ def test_latent_prepare(dtype, heads, q_width, rank, rot, dims, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,q_width,rank,rot,page", [(4, 16, 32, 8, 16), (3, 24, 18, 12, 4), (8, 128, 512, 64, 16)])
+def test_latent_prepare_for_heads_of_their_own_and_gather(dtype, heads, q_width, rank, rot, page):
+    """The other reading of a latent cache: the queries keep their unturned part, and the cached rows of a
+    request's whole context are fetched side by side (the latent part for a product, the turned part into
+    every head's key)."""
+    lens = [(11, 9), (37, 1)]
+    case = _cache_case(dtype, 1, 1, rank + rot, page, lens, seed=2)
+    batch = _Batch(lens)
+    tokens = batch.num_tokens
+    q = randn(tokens, heads, q_width + rot, dtype=dtype, seed=3)
+    kv_rows = randn(tokens, rank + rot, dtype=dtype, seed=4)
+    weight = randn(rank, dtype=dtype, seed=5) + 1.0
+    inv_freq = (1.0 / 50.0 ** (torch.arange(0, max(rot, 2), 2, dtype=torch.float64) / max(rot, 2))).float().to(DEV)
+    results = []
+    for module in (K(), P):
+        cache = case["k_cache"].clone()
+        q_out = torch.zeros(tokens, heads, q_width + rot, dtype=dtype, device=DEV)
+        module.latent_prepare(kv_rows, weight, 1e-5, inv_freq, rot, batch, case["table"], cache, q, q_width, q_out,
+                              q_latent=q[:, :, :q_width])
+        results.append((cache, q_out))
+    for got, want in zip(*results):
+        torch.testing.assert_close(got, want, **(F32 if dtype == torch.float32 else tol(dtype)))
+    cache = results[0][0]
+    totals = [c + n for c, n in lens]
+    src_req = torch.tensor([r for r, n in enumerate(totals) for _ in range(n)], dtype=torch.int32, device=DEV)
+    src_pos = torch.tensor([p for n in totals for p in range(n)], dtype=torch.int32, device=DEV)
+    per_head = q_width + rot + 8
+    for module in (K(), P):
+        latents = torch.zeros(sum(totals) + 1, rank, dtype=dtype, device=DEV)
+        module.gather_cached_rows(cache, case["table"], src_req, src_pos, 0, rank, latents[1:])
+        wide = torch.zeros(sum(totals) + 1, heads * per_head, dtype=dtype, device=DEV)
+        module.gather_cached_rows(cache, case["table"], src_req, src_pos, rank, rot, wide[1:, q_width:], copies=heads,
+                                  head_stride=per_head)
+        results.append((latents, wide))
+    for got, want in zip(results[2], results[3]):
+        assert torch.equal(got, want)
+    assert K().read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(4, 2, 16, 24, 16), (3, 1, 20, 12, 4), (8, 2, 128, 256, 16)])
 def test_head_norm_and_cache_row(dtype, heads, kv_heads, dim, vdim, page):
     lens = [(3, 6), (40, 1), (0, 17)]

@@ -22,6 +22,7 @@
 #include "common.cuh"
 
 #define MP_THREADS 128
+#define LP_HEADS 8      // query heads a block of latent_prepare handles
 
 template <typename T>
 __global__ void __launch_bounds__(MP_THREADS)
@@ -39,8 +40,8 @@ latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const 
   const float fpos = (float)pos;
   const int row_width = rank + rot;     // of a cached row
   const int q_row = lead + rot;         // of a row of q_out: `lead` entries the caller fills or q_latent gives, then the turned part
-  // blockIdx.y: a query head, or (the last one) the token's cached row
-  if (blockIdx.y == heads) {
+  // blockIdx.y: a group of LP_HEADS query heads, or (the last one) the token's cached row
+  if (blockIdx.y == gridDim.y - 1) {
     if (!write) return;
     const T* src = kv_rows + (size_t)t * kv_stride;
     float ss = 0.0f;
@@ -71,37 +72,51 @@ latent_prepare_kernel(const T* __restrict__ kv_rows, long long kv_stride, const 
     }
     return;
   }
-  // a query row: the turned position part behind the latent part
-  const int h = blockIdx.y;
-  for (int j = threadIdx.x; j < rot / 2; j += MP_THREADS) {
-    const T* src = q + (size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width;
-    float u = to_float(src[2 * j]), v = to_float(src[2 * j + 1]);
-    if (2 * j < dims) {
-      float s, c;
-      sincosf(fpos * inv_freq[j], &s, &c);
-      const float nu = u * c - v * s, nv = v * c + u * s;
-      u = nu; v = nv;
+  // query rows of LP_HEADS heads: the turned position part behind the leading part.  The angles depend on
+  // the token only: their cos/sin are made once a block.
+  __shared__ float cs[2][MP_THREADS];
+  const int h0 = blockIdx.y * LP_HEADS, h1 = min(heads, h0 + LP_HEADS);
+  const int pairs = rot / 2;
+  for (int base = 0; base < pairs; base += MP_THREADS) {
+    const int mine = base + threadIdx.x;
+    if (mine < pairs) {
+      float s = 0.0f, c = 1.0f;
+      if (2 * mine < dims) sincosf(fpos * inv_freq[mine], &s, &c);
+      cs[0][threadIdx.x] = c;
+      cs[1][threadIdx.x] = s;
     }
-    T* dst = q_out + ((size_t)t * heads + h) * q_row + lead;
-    dst[2 * j] = from_float<T>(u);
-    dst[2 * j + 1] = from_float<T>(v);
+    __syncthreads();
+    const int here = min(MP_THREADS, pairs - base);
+    for (int i = threadIdx.x; i < (h1 - h0) * here; i += MP_THREADS) {
+      const int h = h0 + i / here, j = i % here;
+      const T* src = q + (size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + 2 * (base + j);
+      const float u = to_float(src[0]), v = to_float(src[1]);
+      T* dst = q_out + ((size_t)t * heads + h) * q_row + lead + 2 * (base + j);
+      dst[0] = from_float<T>(u * cs[0][j] - v * cs[1][j]);
+      dst[1] = from_float<T>(v * cs[0][j] + u * cs[1][j]);
+    }
+    __syncthreads();
   }
-  if ((rot & 1) && threadIdx.x == 0)
-    q_out[((size_t)t * heads + h) * q_row + lead + rot - 1] =
-        q[(size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + rot - 1];
+  if (rot & 1)
+    for (int h = h0 + threadIdx.x; h < h1; h += MP_THREADS)
+      q_out[((size_t)t * heads + h) * q_row + lead + rot - 1] =
+          q[(size_t)t * q_token_stride + (size_t)h * q_head_stride + q_width + rot - 1];
   if (q_latent != nullptr) {
-    const T* src = q_latent + (size_t)t * ql_token_stride + (size_t)h * ql_head_stride;
-    T* dst = q_out + ((size_t)t * heads + h) * q_row;
     constexpr int N = Vec16<T>::N;
-    if (lead % N == 0 && q_row % N == 0 && ql_token_stride % N == 0 && ql_head_stride % N == 0 &&
-        aligned16(q_latent) && aligned16(q_out)) {
-      for (int j = threadIdx.x * N; j < lead; j += MP_THREADS * N) {
+    const bool vec = lead % N == 0 && q_row % N == 0 && ql_token_stride % N == 0 && ql_head_stride % N == 0 &&
+                     aligned16(q_latent) && aligned16(q_out);
+    const int per = vec ? lead / N : lead;
+    for (int i = threadIdx.x; i < (h1 - h0) * per; i += MP_THREADS) {
+      const int h = h0 + i / per, j = (i % per) * (vec ? N : 1);
+      const T* src = q_latent + (size_t)t * ql_token_stride + (size_t)h * ql_head_stride + j;
+      T* dst = q_out + ((size_t)t * heads + h) * q_row + j;
+      if (vec) {
         Vec16<T> v;
-        v.load(src + j);
-        v.store(dst + j);
+        v.load(src);
+        v.store(dst);
+      } else {
+        *dst = *src;
       }
-    } else {
-      for (int j = threadIdx.x; j < lead; j += MP_THREADS) dst[j] = src[j];
     }
   }
 }
@@ -119,12 +134,12 @@ extern "C" int kvb_latent_prepare(const void* kv_rows, long long kv_stride, cons
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "latent_prepare: no status word");
   if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<float>), dim3(tokens, heads + 1), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<float>), dim3(tokens, (heads + LP_HEADS - 1) / LP_HEADS + 1), dim3(MP_THREADS), 0, stream, true,
         (const float*)kv_rows, kv_stride, (const float*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
         table_stride, (float*)cache, page_size, num_pages, write, (const float*)q, q_token_stride, q_head_stride,
         q_width, (const float*)q_latent, ql_token_stride, ql_head_stride, (float*)q_out, heads, rank, rot, lead, status));
   else
-    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<bf16>), dim3(tokens, heads + 1), dim3(MP_THREADS), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((latent_prepare_kernel<bf16>), dim3(tokens, (heads + LP_HEADS - 1) / LP_HEADS + 1), dim3(MP_THREADS), 0, stream, true,
         (const bf16*)kv_rows, kv_stride, (const bf16*)norm_weight, eps, inv_freq, dims, positions, req_index, table,
         table_stride, (bf16*)cache, page_size, num_pages, write, (const bf16*)q, q_token_stride, q_head_stride,
         q_width, (const bf16*)q_latent, ql_token_stride, ql_head_stride, (bf16*)q_out, heads, rank, rot, lead, status));
@@ -290,19 +305,29 @@ extern "C" int kvb_maps_combine(void* out, const float* a, long long rows, int w
   return 0;
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void sigmoid_gate_mul_kernel(T* __restrict__ out, const T* __restrict__ o, long long o_token_stride,
                                         long long o_head_stride, const T* __restrict__ g, long long g_stride,
                                         long long count, int heads, int width) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_GATE_MUL);
+  constexpr int N = VEC ? Vec16<T>::N : 1;     // entries a thread handles at once (they never straddle a head)
   const long long step = (long long)gridDim.x * blockDim.x;
   const int per_token = heads * width;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += step) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * N; i < count; i += step * N) {
     const long long t = i / per_token;
     const int c = (int)(i % per_token), h = c / width, j = c % width;
-    const float value = to_float(o[t * o_token_stride + (long long)h * o_head_stride + j]);
-    const float gate = to_float(g[t * g_stride + c]);
-    out[i] = from_float<T>(value / (1.0f + expf(-gate)));
+    const T* value = o + t * o_token_stride + (long long)h * o_head_stride + j;
+    const T* gate = g + t * g_stride + c;
+    if (VEC) {
+      Vec16<T> a, b;
+      a.load(value);
+      b.load(gate);
+#pragma unroll
+      for (int n = 0; n < N; ++n) a.set(n, a.get(n) / (1.0f + __expf(-b.get(n))));
+      a.store(out + i);
+    } else {
+      out[i] = from_float<T>(to_float(*value) / (1.0f + expf(-to_float(*gate))));
+    }
   }
 }
 
@@ -312,14 +337,21 @@ extern "C" int kvb_sigmoid_gate_mul(void* out, const void* o, long long o_token_
   const long long count = (long long)tokens * heads * width;
   if (count == 0) return 0;
   const int threads = 256;
-  const long long wanted = (count + threads - 1) / threads;
+  const long long wanted = (count / (dtype == KVB_BF16 ? 8 : 1) + threads - 1) / threads + 1;
   const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
   const int blocks = (int)(wanted < resident ? wanted : resident);
+  // bf16 rows made of 16-byte vectors: eight entries a thread (the activation type's rounding hides the fast
+  // exponential); everything else one entry a thread with the exact one
+  const bool vec = dtype == KVB_BF16 && width % 8 == 0 && o_token_stride % 8 == 0 && o_head_stride % 8 == 0 &&
+                   g_stride % 8 == 0 && aligned16(out) && aligned16(o) && aligned16(g);
   if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<float, false>), dim3(blocks), dim3(threads), 0, stream, true,
         (float*)out, (const float*)o, o_token_stride, o_head_stride, (const float*)g, g_stride, count, heads, width));
+  else if (vec)
+    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<bf16, true>), dim3(blocks), dim3(threads), 0, stream, true,
+        (bf16*)out, (const bf16*)o, o_token_stride, o_head_stride, (const bf16*)g, g_stride, count, heads, width));
   else
-    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true,
+    KVB_CHECK_CUDA(kvb_launch((sigmoid_gate_mul_kernel<bf16, false>), dim3(blocks), dim3(threads), 0, stream, true,
         (bf16*)out, (const bf16*)o, o_token_stride, o_head_stride, (const bf16*)g, g_stride, count, heads, width));
   KVB_CHECK_LAUNCH();
   return 0;

@@ -63,7 +63,8 @@ CONFIGS = {
         L(heads=3, dim=24, rot_dim=0, vdim=10, kv_rank=18, ff=None),
         D(heads=2, kv_heads=2, dim=20, vdim=20, diff=0.5, kv_from=0, scale=0.4),
         D(heads=1, kv_heads=1, dim=36, vdim=12, diff=0.2),
-        D(heads=3, kv_heads=1, dim=36, vdim=12, diff=0.9, kv_from=4, ff=24),
+        D(heads=3, kv_heads=1, dim=36, vdim=12, diff=0.9, kv_from=4, ff=20),
+        D(heads=4, kv_heads=2, dim=20, vdim=20, diff=0.3, kv_from=0),          # a second reader of layer 0's cache
     ], vocab=61, width=40, eps=1e-6),
     # sizes the tensor-core kernels take (widths in steps of 16), several pages and key tiles
     "serving_sizes": P.model_config([
@@ -126,15 +127,15 @@ def test_config_names_the_tensors_of_the_plain_statement():
 def test_config_gives_every_constant_to_the_parts():
     cfg = CONFIGS["coincide"]
     spec = model_spec_from_config(cfg)
-    assert [entry.cache_of for entry in spec.schedule] == [None, None, None, 0, None, 4]
+    assert [entry.cache_of for entry in spec.schedule] == [None, None, None, 0, None, 4, 0]
     latent = spec.layers[1].mixer.params
     assert (latent["rot_dim"], latent["rot_dims"], latent["kv_rank"], latent["rot_base"]) == (12, 4, 8, 10000.0)
     borrowed = spec.layers[3].mixer.params
     assert (borrowed["own_kv"], borrowed["scale"], borrowed["diff"], borrowed["eps"]) == (False, 0.4, 0.5, 1e-6)
     assert spec.layers[0].feed_forward is None and "feed_forward_norm" not in spec.layers[0].norms
-    assert spec.layers[5].feed_forward.params["intermediate_size"] == 24
-    assert [layer.block.params["depth"] for layer in spec.layers] == [1, 2, 3, 4, 5, 6]
-    assert {layer.block.params["depth_slots"] for layer in spec.layers} == {7}
+    assert spec.layers[5].feed_forward.params["intermediate_size"] == 20
+    assert [layer.block.params["depth"] for layer in spec.layers] == [1, 2, 3, 4, 5, 6, 7]
+    assert {layer.block.params["depth_slots"] for layer in spec.layers} == {8}
 
 
 @pytest.mark.parametrize("change,message", [

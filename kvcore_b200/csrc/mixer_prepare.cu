@@ -205,13 +205,18 @@ extern "C" int kvb_gather_cached_rows(void* dst, long long dst_row_stride, long 
   return 0;
 }
 
+// Four neighbouring entries, loaded and stored as one access.
+template <typename T>
+struct __align__(4 * sizeof(T)) Quad { T v[4]; };
+#define HN_KEEP 4     // quads a lane keeps of a vector (vectors up to 512 entries; longer ones go entry by entry)
+
 template <typename T>
 __global__ void __launch_bounds__(MP_THREADS)
 head_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const T* __restrict__ q_weight,
                           const T* __restrict__ k_weight, float eps, const int* __restrict__ positions,
                           const int* __restrict__ req_index, const int* __restrict__ table, int table_stride,
                           T* __restrict__ cache, int page_size, int num_pages, int write, int q_vectors,
-                          int k_vectors, int dim, int v_width, int* status) {
+                          int k_vectors, int dim, int v_width, int per_block, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_HEAD_NORM_KV);
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   T* row = rows + (size_t)t * row_stride;
@@ -226,24 +231,65 @@ head_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const T* _
     }
   }
   const int vectors = q_vectors + (write ? k_vectors : 0);
-  // blockIdx.y: a group of four vectors (one a warp); the block of the first group also copies the values
-  for (int n = blockIdx.y * (MP_THREADS / 32) + warp; n < vectors; n = vectors) {
+  // four neighbouring entries a lane and load where the vectors allow it (8 bytes of bf16, 16 of float)
+  const bool quads = dim % 4 == 0 && v_width % 4 == 0 && row_stride % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(rows) % (4 * sizeof(T))) == 0 &&
+                     (reinterpret_cast<uintptr_t>(cache) % (4 * sizeof(T))) == 0 &&
+                     (reinterpret_cast<uintptr_t>(q_weight) % (4 * sizeof(T))) == 0 &&
+                     (k_weight == nullptr || (reinterpret_cast<uintptr_t>(k_weight) % (4 * sizeof(T))) == 0);
+  // blockIdx.y: a group of `per_block` vectors (one a warp at a time); the block of the first group also copies
+  // the values
+  const int group_end = min(vectors, (int)(blockIdx.y + 1) * per_block);
+  for (int n = blockIdx.y * per_block + warp; n < group_end; n += MP_THREADS / 32) {
     const bool is_q = n < q_vectors;
     T* vec = row + (size_t)n * dim;
     const T* w = is_q ? q_weight : k_weight;
+    T* o = is_q ? vec : (dst == nullptr ? nullptr : dst + (size_t)(n - q_vectors) * dim);
     float ss = 0.0f;
+    if (quads && dim <= 4 * 32 * HN_KEEP) {
+      Quad<T> mine[HN_KEEP];
+#pragma unroll
+      for (int s = 0; s < HN_KEEP; ++s) {
+        const int i = (lane + 32 * s) * 4;
+        if (i < dim) {
+          mine[s] = *reinterpret_cast<const Quad<T>*>(vec + i);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float v = to_float(mine[s].v[j]); ss = fmaf(v, v, ss); }
+        }
+      }
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+      if (o != nullptr) {
+#pragma unroll
+        for (int s = 0; s < HN_KEEP; ++s) {
+          const int i = (lane + 32 * s) * 4;
+          if (i < dim) {
+            const Quad<T> wq = *reinterpret_cast<const Quad<T>*>(w + i);
+            Quad<T> r;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r.v[j] = from_float<T>(to_float(mine[s].v[j]) * inv * to_float(wq.v[j]));
+            *reinterpret_cast<Quad<T>*>(o + i) = r;
+          }
+        }
+      }
+      continue;
+    }
     for (int i = lane; i < dim; i += 32) {
       const float v = to_float(vec[i]);
       ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
-    T* o = is_q ? vec : (dst == nullptr ? nullptr : dst + (size_t)(n - q_vectors) * dim);
     if (o != nullptr)
       for (int i = lane; i < dim; i += 32) o[i] = from_float<T>(to_float(vec[i]) * inv * to_float(w[i]));
   }
   if (dst != nullptr && blockIdx.y == 0) {
     const T* v = row + (size_t)(q_vectors + k_vectors) * dim;
-    for (int i = threadIdx.x; i < v_width; i += MP_THREADS) dst[(size_t)k_vectors * dim + i] = v[i];
+    T* out = dst + (size_t)k_vectors * dim;
+    if (quads) {
+      for (int i = threadIdx.x * 4; i < v_width; i += MP_THREADS * 4)
+        *reinterpret_cast<Quad<T>*>(out + i) = *reinterpret_cast<const Quad<T>*>(v + i);
+    } else {
+      for (int i = threadIdx.x; i < v_width; i += MP_THREADS) out[i] = v[i];
+    }
   }
 }
 
@@ -256,16 +302,20 @@ extern "C" int kvb_head_norm_kv_write(void* rows, long long row_stride, const vo
   KVB_REQUIRE(q_vectors > 0 && k_vectors > 0 && dim > 0 && v_width > 0, "head_norm_kv_write: bad sizes");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "head_norm_kv_write: no status word");
-  const int groups = (q_vectors + (write ? k_vectors : 0) + MP_THREADS / 32 - 1) / (MP_THREADS / 32);
+  // few tokens (decoding): four vectors a block, so that the step's few rows spread over the GPU; many tokens: a
+  // block a token walks all its vectors (a block of one vector a warp is over before it has paid for its launch)
+  const int vectors = q_vectors + (write ? k_vectors : 0);
+  const int per_block = tokens >= 512 ? ((vectors + 3) / 4) * 4 : MP_THREADS / 32;
+  const int groups = (vectors + per_block - 1) / per_block;
   KVB_REQUIRE(groups <= 65535, "head_norm_kv_write: too many vectors a token");
   if (dtype == KVB_F32)
     KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<float>), dim3(tokens, groups), dim3(MP_THREADS), 0, stream, true,
         (float*)rows, row_stride, (const float*)q_weight, (const float*)k_weight, eps, positions, req_index, table,
-        table_stride, (float*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
+        table_stride, (float*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, per_block, status));
   else
     KVB_CHECK_CUDA(kvb_launch((head_norm_kv_write_kernel<bf16>), dim3(tokens, groups), dim3(MP_THREADS), 0, stream, true,
         (bf16*)rows, row_stride, (const bf16*)q_weight, (const bf16*)k_weight, eps, positions, req_index, table,
-        table_stride, (bf16*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, status));
+        table_stride, (bf16*)cache, page_size, num_pages, write, q_vectors, k_vectors, dim, v_width, per_block, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }

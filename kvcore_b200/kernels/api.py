@@ -1127,7 +1127,15 @@ def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_
             if run.max_query_len == 1:       # decoded tokens only: fill the GPU by cutting the keys
                 bound = getattr(run, "max_seq_len_bound", 0) or run.max_seq_len
                 tiles = 1 if split_mode else -(-max_rows // 64)
-                splits = decode_splits(run.num_reqs * tiles, value_heads * maps * slices, bound, sm_count(q.device))
+                # Measured in whole steps (batch 8 and 64 at 2,048 tokens, both cache layouts): beyond one wave
+                # of blocks (two fit a multiprocessor, as of the TMA decode kernel) that kernel's policy of
+                # evening out the last wave; below it the fewer chunks of the two policies (every chunk costs a
+                # block's start, a partial result and a share of the combine)
+                sms = sm_count(q.device)
+                items, heads_here = run.num_reqs * tiles, value_heads * maps * slices
+                splits = decode_splits_tma(items, heads_here, bound, sms)
+                if items * heads_here * 2 <= sms * TMA_DECODE_BLOCKS_PER_SM:
+                    splits = min(splits, decode_splits(items, heads_here, bound, sms))
         scratch = None
         if splits > 1:
             tile_m, tiles = (16, 1) if split_mode else (64, -(-max_rows // 64))

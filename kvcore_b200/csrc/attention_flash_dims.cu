@@ -8,8 +8,9 @@
 // reuse every K/V tile.  Two shapes of one kernel body:
 //   * TILE (prompt portions, many heads a key head): 64 rows a block, 16 a warp; every warp scores all
 //     keys of a K tile.
-//   * SPLIT (at most 16 rows a key head: decode): the 4 warps take a quarter of every K tile's keys each and
-//     merge their partial (max, sum, output) through shared memory.
+//   * SPLIT (at most 16 or 32 rows a key head: decode): the warps form RG row groups of 16 rows (RG = 1 or 2)
+//     times 4 / RG key groups; a key group takes its share of every K tile's keys, and the key groups of a
+//     row group merge their partial (max, sum, output) through shared memory.
 // In both, the key range of a request may be cut into `num_splits` contiguous chunks (one block each);
 // partial results then go to scratch and a second kernel combines them.
 //
@@ -112,14 +113,16 @@ __device__ __forceinline__ void fd_load_tile(bf16* ks, bf16* vs, const FlashDims
   }
 }
 
-template <int DVB, int KEYS, bool SPLIT>
+template <int DVB, int KEYS, int RG>      // RG: row groups of the few-row form (1 or 2), 0 for 64-row tiles
 __global__ void __launch_bounds__(FD_THREADS)
 flash_dims_kernel(const FlashDimsParams p) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_FLASH_DIMS);
-  constexpr int TILE_M = SPLIT ? 16 : 64;
+  constexpr bool SPLIT = RG > 0;
+  constexpr int KG = SPLIT ? 4 / RG : 1;             // key groups of warps
+  constexpr int TILE_M = SPLIT ? 16 * RG : 64;
   constexpr int VROW = DVB + FD_PAD;
   constexpr int DBLOCKS = DVB / 8;
-  constexpr int WARP_KEYS = SPLIT ? KEYS / 4 : KEYS;
+  constexpr int WARP_KEYS = KEYS / KG;
   constexpr int NB = WARP_KEYS / 8;
   static_assert(NB >= 2 && NB % 2 == 0, "a warp scores at least 16 keys of a tile");
   const int DK = p.DK, krow = DK + FD_PAD, ksteps = DK / 16;
@@ -188,7 +191,7 @@ flash_dims_kernel(const FlashDimsParams p) {
   fd_wait<1>();
   __syncthreads();
 
-  const int wrow = SPLIT ? 0 : warp * 16;  // first row of this warp inside the block's tile
+  const int wrow = SPLIT ? (warp % (SPLIT ? RG : 1)) * 16 : warp * 16;  // first row of this warp inside the block's tile
   int row_pos[2];
   bool row_valid[2];
   int row_head[2];
@@ -204,8 +207,8 @@ flash_dims_kernel(const FlashDimsParams p) {
 #pragma unroll
   for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
-  // the sink joins the denominator once: in the first chunk of keys, and (SPLIT) in the first warp only
-  if (p.sink != nullptr && split == 0 && (!SPLIT || warp == 0)) {
+  // the sink joins the denominator once: in the first chunk of keys, and (SPLIT) in the first key group only
+  if (p.sink != nullptr && split == 0 && (!SPLIT || warp / (SPLIT ? RG : 1) == 0)) {
 #pragma unroll
     for (int h = 0; h < 2; ++h)
       if (row_valid[h]) {
@@ -226,7 +229,7 @@ flash_dims_kernel(const FlashDimsParams p) {
     if (t + 2 < tile_end)
       fd_lookup_rows<KEYS>(k_rows + buf * KEYS, v_rows + buf * KEYS, p, pages, kh, vh, v_col, (t + 2) * KEYS, key_lo, key_hi);
 
-    const int wkey = SPLIT ? warp * WARP_KEYS : 0;  // first key of the tile this warp scores
+    const int wkey = SPLIT ? (warp / (SPLIT ? RG : 1)) * WARP_KEYS : 0;  // first key of the tile this warp scores
     float s[NB][4];
 #pragma unroll
     for (int j = 0; j < NB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
@@ -345,7 +348,7 @@ flash_dims_kernel(const FlashDimsParams p) {
     return;
   }
 
-  // ---- SPLIT: merge the four warps (each saw other keys of the same 16 rows) -------------------------
+  // ---- SPLIT: merge the key groups of every row group (each saw other keys of the same 16 rows) ---------
   __syncthreads();
   float* merge_o = reinterpret_cast<float*>(ks);            // [4 warps][16 rows][DVB]
   float* merge_ml = merge_o + 4 * 16 * DVB;                 // [4 warps][16 rows][2]
@@ -364,19 +367,22 @@ flash_dims_kernel(const FlashDimsParams p) {
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < 16 * DVB; i += FD_THREADS) {
+  constexpr int GROUPS = SPLIT ? RG : 1;
+  for (int i = threadIdx.x; i < TILE_M * DVB; i += FD_THREADS) {
     const int r = i / DVB, d = i % DVB;
     if (r >= rows_total || d >= v_cols) continue;
+    const int group = r / 16, rr = r % 16;     // the row's warps are group, group + GROUPS, ...
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    for (int kg = 0; kg < KG; ++kg) m = fmaxf(m, merge_ml[((kg * GROUPS + group) * 16 + rr) * 2]);
     float total = 0.0f, acc = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = merge_ml[(w * 16 + r) * 2];
+    for (int kg = 0; kg < KG; ++kg) {
+      const int w = kg * GROUPS + group;
+      const float mw = merge_ml[(w * 16 + rr) * 2];
       const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
-      total += merge_ml[(w * 16 + r) * 2 + 1] * f;
-      acc += merge_o[((size_t)(w * 16 + r)) * DVB + d] * f;
+      total += merge_ml[(w * 16 + rr) * 2 + 1] * f;
+      acc += merge_o[((size_t)(w * 16 + rr)) * DVB + d] * f;
     }
     if (p.num_splits == 1) {
       const int token = q_begin + r / p.G;
@@ -386,10 +392,10 @@ flash_dims_kernel(const FlashDimsParams p) {
       if (p.out_f32) ((float*)p.out)[off] = value;
       else ((bf16*)p.out)[off] = __float2bfloat16_rn(value);
     } else {
-      p.partial_o[(slot * 16 + r) * DVB + d] = acc;
+      p.partial_o[(slot * TILE_M + r) * DVB + d] = acc;
       if (d == 0) {
-        p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
-        p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
+        p.partial_ml[(slot * TILE_M + r) * 2 + 0] = m;
+        p.partial_ml[(slot * TILE_M + r) * 2 + 1] = total;
       }
     }
   }
@@ -434,9 +440,10 @@ __global__ void flash_dims_combine_kernel(const FlashDimsParams p, int tile_m) {
   else ((bf16*)p.out)[off] = __float2bfloat16_rn(value);
 }
 
-template <int DVB, int KEYS, bool SPLIT>
+template <int DVB, int KEYS, int RG>
 static int fd_launch_shape(const FlashDimsParams& p, int max_rows, cudaStream_t stream) {
-  constexpr int TILE_M = SPLIT ? 16 : 64;
+  constexpr bool SPLIT = RG > 0;
+  constexpr int TILE_M = SPLIT ? 16 * RG : 64;
   const int krow = p.DK + FD_PAD;
   size_t smem = 4 * KEYS * sizeof(long long) + (size_t)(TILE_M + 2 * KEYS) * krow * sizeof(bf16);
   if (!p.v_in_k) smem += (size_t)2 * KEYS * (DVB + FD_PAD) * sizeof(bf16);
@@ -448,12 +455,12 @@ static int fd_launch_shape(const FlashDimsParams& p, int max_rows, cudaStream_t 
   KVB_REQUIRE(smem <= 227 * 1024, "flash_dims: the tiles do not fit in shared memory");
   static size_t configured = 0;   // grows only; the first call of a size is never inside a graph capture
   if (smem > configured) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_dims_kernel<DVB, KEYS, SPLIT>,
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_dims_kernel<DVB, KEYS, RG>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid(p.tiles * p.num_splits, p.KH * p.vsplit, p.num_reqs);
-  KVB_CHECK_CUDA(kvb_launch((flash_dims_kernel<DVB, KEYS, SPLIT>), dim3(grid), dim3(FD_THREADS), smem, stream, true, p));
+  KVB_CHECK_CUDA(kvb_launch((flash_dims_kernel<DVB, KEYS, RG>), dim3(grid), dim3(FD_THREADS), smem, stream, true, p));
   KVB_CHECK_LAUNCH();
   if (p.num_splits > 1) {
     const long long elements = (long long)(max_rows < p.tiles * TILE_M ? max_rows : p.tiles * TILE_M) * DVB;
@@ -465,13 +472,14 @@ static int fd_launch_shape(const FlashDimsParams& p, int max_rows, cudaStream_t 
 }
 
 template <int DVB>
-static int fd_launch(const FlashDimsParams& p, bool split_mode, int max_rows, cudaStream_t stream) {
-  if (split_mode) return fd_launch_shape<DVB, 64, true>(p, max_rows, stream);
+static int fd_launch(const FlashDimsParams& p, int row_groups, int max_rows, cudaStream_t stream) {
+  if (row_groups == 1) return fd_launch_shape<DVB, 64, 1>(p, max_rows, stream);
+  if (row_groups == 2) return fd_launch_shape<DVB, 64, 2>(p, max_rows, stream);
   // tiles of 64 keys while two blocks of them fit a multiprocessor's shared memory, else tiles of 32
   size_t wide = 4 * 64 * sizeof(long long) + (size_t)(64 + 2 * 64) * (p.DK + FD_PAD) * sizeof(bf16);
   if (!p.v_in_k) wide += (size_t)2 * 64 * (DVB + FD_PAD) * sizeof(bf16);
-  if (wide > 113 * 1024) return fd_launch_shape<DVB, 32, false>(p, max_rows, stream);
-  return fd_launch_shape<DVB, 64, false>(p, max_rows, stream);
+  if (wide > 113 * 1024) return fd_launch_shape<DVB, 32, 0>(p, max_rows, stream);
+  return fd_launch_shape<DVB, 64, 0>(p, max_rows, stream);
 }
 
 // The value width a block accumulates for a value width DV, and the number of slices (0: not taken).
@@ -487,13 +495,12 @@ extern "C" int kvb_flash_dims_block_width(int DV, int* slices) {
 }
 
 // Scratch floats for `num_splits` chunks of keys: partial outputs, then partial (max, sum).
-extern "C" long long kvb_flash_dims_scratch_floats(int num_reqs, int KH, int DV, int max_rows, int split_mode,
-                                                   int num_splits) {
+extern "C" long long kvb_flash_dims_scratch_floats(int num_reqs, int KH, int DV, int max_rows, int num_splits) {
   if (num_splits <= 1) return 0;
   int slices = 0;
   const int dvb = kvb_flash_dims_block_width(DV, &slices);
-  const int tile_m = split_mode ? 16 : 64;
-  const long long tiles = split_mode ? 1 : (max_rows + tile_m - 1) / tile_m;
+  const int tile_m = max_rows <= 16 ? 16 : max_rows <= 32 ? 32 : 64;
+  const long long tiles = (max_rows + tile_m - 1) / tile_m;
   return (long long)num_reqs * KH * slices * tiles * num_splits * tile_m * (dvb + 2);
 }
 
@@ -537,23 +544,23 @@ extern "C" int kvb_flash_dims_attention(void* out, long long out_token_stride, l
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "flash_dims: no status word");
   const int max_rows = max_query_len * group;
-  const bool split_mode = max_rows <= 16;
-  p.tiles = split_mode ? 1 : (max_rows + 63) / 64;
+  const int row_groups = max_rows <= 16 ? 1 : max_rows <= 32 ? 2 : 0;   // the few-row form, or 64-row tiles
+  p.tiles = row_groups ? 1 : (max_rows + 63) / 64;
   p.num_splits = num_splits < 1 ? 1 : num_splits;
   KVB_REQUIRE(p.num_splits <= KVB_MAX_SPLITS, "flash_dims: at most 1024 splits");
   KVB_REQUIRE(p.num_splits == 1 || scratch != nullptr, "flash_dims: splits need scratch memory");
   KVB_REQUIRE(num_reqs <= 65535 && p.KH * p.vsplit <= 65535, "flash_dims: batch too large for one launch");
   p.partial_o = scratch;
-  const int tile_m = split_mode ? 16 : 64;
+  const int tile_m = row_groups ? 16 * row_groups : 64;
   p.partial_ml = scratch == nullptr ? nullptr
       : scratch + (size_t)num_reqs * p.KH * p.vsplit * p.tiles * p.num_splits * tile_m * dvb;
   switch (dvb) {
-    case 32: return fd_launch<32>(p, split_mode, max_rows, stream);
-    case 64: return fd_launch<64>(p, split_mode, max_rows, stream);
-    case 96: return fd_launch<96>(p, split_mode, max_rows, stream);
-    case 128: return fd_launch<128>(p, split_mode, max_rows, stream);
-    case 192: return fd_launch<192>(p, split_mode, max_rows, stream);
-    default: return fd_launch<256>(p, split_mode, max_rows, stream);
+    case 32: return fd_launch<32>(p, row_groups, max_rows, stream);
+    case 64: return fd_launch<64>(p, row_groups, max_rows, stream);
+    case 96: return fd_launch<96>(p, row_groups, max_rows, stream);
+    case 128: return fd_launch<128>(p, row_groups, max_rows, stream);
+    case 192: return fd_launch<192>(p, row_groups, max_rows, stream);
+    default: return fd_launch<256>(p, row_groups, max_rows, stream);
   }
 }
 

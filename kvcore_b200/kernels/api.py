@@ -1062,9 +1062,11 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
     return out
 
 
-def _flash_dims_geometry(key_width: int, value_width: int, split_mode: bool, values_in_keys: bool):
+def _flash_dims_geometry(key_width: int, value_width: int, tile_rows: int, values_in_keys: bool):
     """(value width a block accumulates, slices of the value width, shared-memory bytes) of the tensor-core
-    kernel for separate key and value widths, or None when it does not take them."""
+    kernel for separate key and value widths, or None when it does not take them.  ``tile_rows``: 64 for
+    prompt tiles, 16 or 32 for the few-row form of decode steps."""
+    split_mode = tile_rows < 64
     if key_width % 16 or not 16 <= key_width <= 1024 or value_width % 8 or not 8 <= value_width <= 1024:
         return None
     slices = -(-value_width // 256)
@@ -1073,7 +1075,7 @@ def _flash_dims_geometry(key_width: int, value_width: int, split_mode: bool, val
     if block is None:
         return None
     values_in_keys = values_in_keys and slices * block <= key_width
-    tile_m = 16 if split_mode else 64
+    tile_m = tile_rows
 
     def tiles_bytes(keys_per_tile: int) -> int:
         total = 4 * keys_per_tile * 8 + (tile_m + 2 * keys_per_tile) * (key_width + 8) * 2
@@ -1099,8 +1101,7 @@ def flash_dims_supported(q, out, key_width, value_width, page_size, key_strides,
     if out.stride(0) % 2 or out.stride(1) % 2 or out.data_ptr() % 8:
         return False
     alias = (keys.data_ptr() == values.data_ptr() and tuple(key_strides) == tuple(value_strides) and maps == 1)
-    return (_flash_dims_geometry(key_width, value_width, False, alias) is not None
-            and _flash_dims_geometry(key_width, value_width, True, alias) is not None)
+    return all(_flash_dims_geometry(key_width, value_width, rows, alias) is not None for rows in (64, 32, 16))
 
 
 def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
@@ -1111,16 +1112,17 @@ def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_
     lens = getattr(ctx, "host_query_lens", None)
     contexts = getattr(ctx, "host_context_lens", None)
     runs = [(ctx, table)]
-    if num_splits is None and lens and contexts and len(lens) == ctx.num_reqs and ctx.max_query_len * group > 16:
-        long_count = sum(1 for n in lens if n * group > 16)
-        if 0 < long_count < ctx.num_reqs and all(n * group > 16 for n in lens[:long_count]):
+    if num_splits is None and lens and contexts and len(lens) == ctx.num_reqs and ctx.max_query_len * group > 32:
+        long_count = sum(1 for n in lens if n * group > 32)
+        if 0 < long_count < ctx.num_reqs and all(n * group > 32 for n in lens[:long_count]):
             runs = [(_RequestRun(ctx, begin, end), table[begin:end])
                     for begin, end in ((0, long_count), (long_count, ctx.num_reqs))]
     for run, run_table in runs:
         max_rows = run.max_query_len * group
-        split_mode = max_rows <= 16
+        split_mode = max_rows <= 32                 # the few-row form: 16 or 32 rows a key head
+        tile_m = 16 if max_rows <= 16 else 32 if split_mode else 64
         alias = keys.data_ptr() == values.data_ptr() and tuple(key_strides) == tuple(value_strides) and maps == 1
-        block, slices, _ = _flash_dims_geometry(key_width, value_width, split_mode, alias)
+        block, slices, _ = _flash_dims_geometry(key_width, value_width, tile_m, alias)
         splits = num_splits
         if splits is None:
             splits = 1
@@ -1138,7 +1140,7 @@ def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_
                     splits = min(splits, decode_splits(items, heads_here, bound, sms))
         scratch = None
         if splits > 1:
-            tile_m, tiles = (16, 1) if split_mode else (64, -(-max_rows // 64))
+            tiles = 1 if split_mode else -(-max_rows // 64)
             scratch = torch.empty(run.num_reqs * value_heads * maps * slices * tiles * splits * tile_m * (block + 2),
                                   dtype=torch.float32, device=q.device)
         _call("kvb_flash_dims_attention", out.data_ptr(), out.stride(0), out.stride(1),

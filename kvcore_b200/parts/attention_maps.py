@@ -207,9 +207,9 @@ class LatentAttention(Mixer):
             return 0
         d, r, v, width = self.head_dim, self.rot_dim, self.value_dim, self.kv_cols
         geometry = K.api._flash_dims_geometry
-        if ((d + r) % 16 or (d + r + v) % 8 or v % 8 or geometry(d + r, v, False, False) is None
-                or width % 16 or self.kv_rank % 8 or geometry(width, self.kv_rank, False, True) is None
-                or geometry(width, self.kv_rank, True, True) is None or rows.stride(0) % 8 or self.q_cols % 8):
+        if ((d + r) % 16 or (d + r + v) % 8 or v % 8 or geometry(d + r, v, 64, False) is None
+                or width % 16 or self.kv_rank % 8 or rows.stride(0) % 8 or self.q_cols % 8
+                or any(geometry(width, self.kv_rank, tile_rows, True) is None for tile_rows in (64, 32, 16))):
             return 0
         count = 0
         while count < len(lens) and lens[count] >= self.expand_min_tokens:

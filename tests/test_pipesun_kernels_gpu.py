@@ -247,13 +247,15 @@ DIMS_SHAPES = [
     ("latent", 4, 1, 40, 32, 16, [(0, 33), (64, 1), (15, 2)], True, dict()),
     ("latent", 3, 1, 30, 18, 8, [(9, 9), (100, 1)], True, dict()),                       # general kernel
     ("maps", 8, 2, 64, 128, 16, [(0, 150), (40, 70)], False, dict()),                    # tiles of 64 rows
-    ("maps", 4, 1, 48, 96, 16, [(300, 1), (17, 1), (129, 1), (0, 1)], False, dict()),    # few rows: the warps share the keys
-    ("maps", 4, 1, 48, 96, 16, [(700, 1), (140, 2)], False, dict(num_splits=3)),
+    ("maps", 6, 2, 80, 48, 16, [(300, 1), (17, 1), (129, 1), (0, 1)], False, dict()),    # few rows: the warps share the keys
+    ("maps", 6, 2, 80, 48, 16, [(700, 1), (140, 2)], False, dict(num_splits=3)),
     ("maps", 4, 2, 128, 256, 16, [(10, 200), (400, 1), (133, 1), (30, 2)], False, dict()),  # mixed: two runs, one result
-    ("latent", 8, 1, 112, 96, 16, [(0, 130), (250, 1), (77, 3)], True, dict()),          # the values are columns of the keys
+    ("latent", 6, 1, 144, 120, 16, [(0, 130), (250, 1), (77, 3)], True, dict()),          # the values are columns of the keys
     ("latent", 16, 1, 576, 512, 16, [(0, 100), (90, 45)], True, dict()),                 # two slices of the value width
     ("latent", 16, 1, 576, 512, 16, [(1000, 1), (90, 1), (511, 1)], True, dict()),       # decode, keys cut by the policy
-    ("latent", 32, 1, 320, 256, 32, [(500, 1), (64, 1)], True, dict(num_splits=4)),      # one tile of 64 rows, 4 chunks
+    ("latent", 32, 1, 320, 256, 32, [(500, 1), (64, 1)], True, dict(num_splits=4)),      # 32 rows: two row groups of warps, 4 chunks
+    ("latent", 24, 1, 64, 40, 16, [(900, 1), (3, 1), (70, 1)], True, dict()),            # 24 rows, chunks by the policy
+    ("maps", 12, 1, 32, 64, 16, [(300, 1), (40, 2), (0, 1)], False, dict()),             # 12 and 24 rows, values apart from the keys
     ("latent", 128, 1, 96, 80, 16, [(300, 2), (31, 1)], False, dict(num_splits=2)),      # three tiles, a width below its block's
 ]
 
@@ -290,10 +292,11 @@ EDGES = [
     (torch.float32, "maps", 16, 24, 16, (700, 1), dict()),
     (torch.float32, "latent", 40, 32, 8, (300, 30), dict()),
     (torch.bfloat16, "maps", 20, 12, 4, (300, 1), dict()),                         # general kernel in bfloat16
-    (torch.bfloat16, "maps", 48, 96, 16, (900, 1), dict()),                        # few rows, keys cut by the policy
+    (torch.bfloat16, "maps", 80, 48, 16, (900, 1), dict()),                        # few rows, keys cut by the policy
     (torch.bfloat16, "maps", 64, 128, 16, (100, 201), dict()),                     # tiles
-    (torch.bfloat16, "latent", 112, 96, 16, (640, 1), dict(num_splits=5)),
+    (torch.bfloat16, "latent", 144, 120, 16, (640, 1), dict(num_splits=5)),
     (torch.bfloat16, "latent", 576, 512, 16, (100, 129), dict()),
+    (torch.bfloat16, "latent", 160, 128, 16, (640, 1), dict(heads=24)),            # 24 rows: two row groups of warps
 ]
 
 
@@ -304,7 +307,8 @@ def test_a_key_that_stands_out(dtype, kind, dim, vdim, page, lens, how, place):
     at the first position, on either side of a page's border far back, hundreds of keys back, at the row's
     own position.  The output is that key's value whatever the other keys and the sink say.  Put at the
     position behind the row's own (written, but not visible to it), with a huge value, it leaves no trace."""
-    heads, kv_heads = (2, 1) if kind == "maps" else (4, 1)
+    how = dict(how)
+    heads, kv_heads = (2, 1) if kind == "maps" else (how.pop("heads", 4), 1)
     context, query = lens
     last = context + query - 1
     position = {"first": 0, "page_end": 3 * page - 1, "page_start": 3 * page, "far": last - 257, "own": last,

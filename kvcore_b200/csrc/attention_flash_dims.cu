@@ -233,7 +233,7 @@ flash_dims_kernel(const FlashDimsParams p) {
     float s[NB][4];
 #pragma unroll
     for (int j = 0; j < NB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-#pragma unroll 2
+#pragma unroll 4
     for (int k = 0; k < ksteps; ++k) {
       unsigned qf[4];
       fd_ldmatrix_x4(qf, qs + (wrow + (lane & 7) + 8 * ((lane >> 3) & 1)) * krow + k * 16 + 8 * (lane >> 4));
@@ -475,10 +475,10 @@ template <int DVB>
 static int fd_launch(const FlashDimsParams& p, int row_groups, int max_rows, cudaStream_t stream) {
   if (row_groups == 1) return fd_launch_shape<DVB, 64, 1>(p, max_rows, stream);
   if (row_groups == 2) return fd_launch_shape<DVB, 64, 2>(p, max_rows, stream);
-  // tiles of 64 keys while two blocks of them fit a multiprocessor's shared memory, else tiles of 32
+  // tiles of 64 keys while three blocks of them fit a multiprocessor's shared memory, else tiles of 32
   size_t wide = 4 * 64 * sizeof(long long) + (size_t)(64 + 2 * 64) * (p.DK + FD_PAD) * sizeof(bf16);
   if (!p.v_in_k) wide += (size_t)2 * 64 * (DVB + FD_PAD) * sizeof(bf16);
-  if (wide > 113 * 1024) return fd_launch_shape<DVB, 32, 0>(p, max_rows, stream);
+  if (wide > 75 * 1024) return fd_launch_shape<DVB, 32, 0>(p, max_rows, stream);
   return fd_launch_shape<DVB, 64, 0>(p, max_rows, stream);
 }
 

@@ -170,7 +170,13 @@ extern "C" int kvb_rms_norm_shift(void* out, const void* x, const void* weight, 
   return 0;
 }
 
-template <typename T, typename W, bool KEPT>
+// Four neighbouring entries, loaded and stored as one access.
+template <typename T>
+struct __align__(4 * sizeof(T)) Quad4 { T v[4]; };
+
+// KEPT: 0 rows of any width, read twice; 1 rows up to SN_THREADS * SN_KEEP entries kept in registers; 2 the same
+// with four neighbouring entries a thread and access (widths that are multiples of 4, rows on 16-byte boundaries).
+template <typename T, typename W, int KEPT>
 __global__ void __launch_bounds__(SN_THREADS)
 stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
                        const W* __restrict__ weight, int width, float eps, float* __restrict__ avg,
@@ -181,7 +187,74 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
   const size_t base = (size_t)blockIdx.x * width;
   const T* arow = a + base;
   float ss = 0.0f;
-  if (KEPT) {
+  if (KEPT == 2) {
+    constexpr int PASSES = SN_KEEP / 4;
+    float mine[PASSES][4], stream[PASSES][4], w[PASSES][4];
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s) {
+      const int i = (threadIdx.x + s * SN_THREADS) * 4;
+      if (i < width) {
+        const Quad4<T> qa = *reinterpret_cast<const Quad4<T>*>(arow + i);
+        const Quad4<float> qx = *reinterpret_cast<const Quad4<float>*>(x + base + i);
+        const Quad4<W> qw = *reinterpret_cast<const Quad4<W>*>(weight + i);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mine[s][j] = to_float(qa.v[j]); stream[s][j] = qx.v[j]; w[s][j] = to_float(qw.v[j]);
+          ss = fmaf(mine[s][j], mine[s][j], ss);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mine[s][j] = stream[s][j] = w[s][j] = 0.0f;
+      }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) stream[s][j] = stream[s][j] + mine[s][j] * inv * w[s][j];
+    if (avg != nullptr) {
+#pragma unroll
+      for (int s = 0; s < PASSES; ++s)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mine[s][j] = 0.0f;
+      for (int n = 0; n < count; ++n) {
+        const float c = to_float(coeffs[n]);
+        const float* result = stack + (size_t)n * stack_stride + base;
+#pragma unroll
+        for (int s = 0; s < PASSES; ++s) {
+          const int i = (threadIdx.x + s * SN_THREADS) * 4;
+          if (i < width) {
+            const Quad4<float> qr = *reinterpret_cast<const Quad4<float>*>(result + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mine[s][j] = fmaf(c, qr.v[j], mine[s][j]);
+          }
+        }
+      }
+      const float c = to_float(coeffs[count]);
+#pragma unroll
+      for (int s = 0; s < PASSES; ++s) {
+        const int i = (threadIdx.x + s * SN_THREADS) * 4;
+        if (i < width) {
+          Quad4<float> q;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) q.v[j] = fmaf(c, stream[s][j], mine[s][j]);
+          *reinterpret_cast<Quad4<float>*>(avg + base + i) = q;
+        }
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s) {
+      const int i = (threadIdx.x + s * SN_THREADS) * 4;
+      if (i < width) {
+        Quad4<float> q;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q.v[j] = stream[s][j];
+        *reinterpret_cast<Quad4<float>*>(out + base + i) = q;
+      }
+    }
+    return;
+  }
+  if (KEPT == 1) {
     float mine[SN_KEEP], stream[SN_KEEP], w[SN_KEEP];
 #pragma unroll
     for (int s = 0; s < SN_KEEP; ++s) {
@@ -246,11 +319,17 @@ extern "C" int kvb_stream_add_norm(float* out, const float* x, const void* a, co
   KVB_REQUIRE(avg == nullptr || (coeffs != nullptr && count >= 0 && (count == 0 || stack != nullptr)),
               "stream_add_norm: the depth average needs its coefficients and the results in front");
   cudaError_t err;
+  const bool kept = width <= SN_THREADS * SN_KEEP;
+  const bool quads = kept && width % 4 == 0 && aligned16(out) && aligned16(x) && aligned16(a) && aligned16(weight) &&
+                     (avg == nullptr || (aligned16(avg) && (count == 0 || (aligned16(stack) && stack_stride % 4 == 0))));
 #define KVB_AN_LAUNCH(T, W)                                                                                       \
-  err = width <= SN_THREADS * SN_KEEP                                                                             \
-      ? kvb_launch((stream_add_norm_kernel<T, W, true>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,  \
+  err = quads                                                                                                     \
+      ? kvb_launch((stream_add_norm_kernel<T, W, 2>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
                    (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)  \
-      : kvb_launch((stream_add_norm_kernel<T, W, false>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x, \
+      : kept                                                                                                      \
+      ? kvb_launch((stream_add_norm_kernel<T, W, 1>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
+                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)  \
+      : kvb_launch((stream_add_norm_kernel<T, W, 0>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
                    (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)
   if (dtype == KVB_F32 && weight_dtype == KVB_F32) KVB_AN_LAUNCH(float, float);
   else if (dtype == KVB_F32) KVB_AN_LAUNCH(float, bf16);

@@ -1081,8 +1081,8 @@ def _flash_dims_geometry(key_width: int, value_width: int, tile_rows: int, value
         total = 4 * keys_per_tile * 8 + (tile_m + 2 * keys_per_tile) * (key_width + 8) * 2
         return total if values_in_keys else total + 2 * keys_per_tile * (block + 8) * 2
 
-    # prompts: tiles of 64 keys while two blocks of them fit a multiprocessor's shared memory, else of 32
-    keys_per_tile = 64 if split_mode or tiles_bytes(64) <= 113 * 1024 else 32
+    # prompts: tiles of 64 keys while three blocks of them fit a multiprocessor's shared memory, else of 32
+    keys_per_tile = 64 if split_mode or tiles_bytes(64) <= 75 * 1024 else 32
     smem = tiles_bytes(keys_per_tile)
     if split_mode:
         smem = max(smem, 4 * keys_per_tile * 8 + tile_m * (key_width + 8) * 2 + (4 * 16 * block + 128) * 4)

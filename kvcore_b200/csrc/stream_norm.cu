@@ -38,7 +38,13 @@ __device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (
 // bound by the latency of its loads, not by bytes).  Wider rows are read again.
 #define SN_KEEP 16
 
-template <typename IN, typename OUT, typename W, bool KEPT>
+// Four neighbouring entries, loaded and stored as one access.
+template <typename T>
+struct __align__(4 * sizeof(T)) Quad4 { T v[4]; };
+
+// KEPT: 0 rows of any width, read twice; 1 rows kept in registers; 2 the same with four neighbouring entries a
+// thread and access (widths that are multiples of 4, every row on a boundary of four entries).
+template <typename IN, typename OUT, typename W, int KEPT>
 __global__ void __launch_bounds__(SN_THREADS)
 rms_norm_shift_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* __restrict__ weight,
                       const W* __restrict__ shift, float* __restrict__ state, const int* __restrict__ req_index,
@@ -63,7 +69,76 @@ rms_norm_shift_kernel(OUT* __restrict__ out, const IN* __restrict__ x, const W* 
   const IN* prow = shifting && !first ? row - width : nullptr;
   const IN* lrow = first && last != t ? x + (size_t)last * width : nullptr;
   float ss = 0.0f, sp = 0.0f, sl = 0.0f;
-  if (KEPT) {
+  if (KEPT == 2) {
+    constexpr int PASSES = SN_KEEP / 4;
+    float mine[PASSES][4], before[PASSES][4], final_row[PASSES][4], w[PASSES][4], mix[PASSES][4];
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s) {
+      const int i = (threadIdx.x + s * SN_THREADS) * 4;
+      const bool in = i < width;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mine[s][j] = w[s][j] = before[s][j] = final_row[s][j] = mix[s][j] = 0.0f;
+      if (in) {
+        const Quad4<IN> qx = *reinterpret_cast<const Quad4<IN>*>(row + i);
+        const Quad4<W> qw = *reinterpret_cast<const Quad4<W>*>(weight + i);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { mine[s][j] = to_float(qx.v[j]); w[s][j] = to_float(qw.v[j]); }
+        if (shifting) {
+          const Quad4<W> qm = *reinterpret_cast<const Quad4<W>*>(shift + i);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mix[s][j] = to_float(qm.v[j]);
+          if (first) {
+            const Quad4<float> qs = *reinterpret_cast<const Quad4<float>*>(srow + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) before[s][j] = qs.v[j];
+          } else {
+            const Quad4<IN> qp = *reinterpret_cast<const Quad4<IN>*>(prow + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) before[s][j] = to_float(qp.v[j]);
+          }
+          if (lrow != nullptr) {
+            const Quad4<IN> ql = *reinterpret_cast<const Quad4<IN>*>(lrow + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) final_row[s][j] = to_float(ql.v[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        ss = fmaf(mine[s][j], mine[s][j], ss);
+        if (prow != nullptr) sp = fmaf(before[s][j], before[s][j], sp);
+        sl = fmaf(final_row[s][j], final_row[s][j], sl);
+      }
+    block_sum3(ss, sp, sl, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    const float inv_p = 1.0f / sqrtf(sp / (float)width + eps);
+    const float inv_l = 1.0f / sqrtf(sl / (float)width + eps);
+#pragma unroll
+    for (int s = 0; s < PASSES; ++s) {
+      const int i = (threadIdx.x + s * SN_THREADS) * 4;
+      if (i >= width) continue;
+      Quad4<OUT> result;
+      Quad4<float> kept_row;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y = mine[s][j] * inv * w[s][j];
+        float r = y;
+        if (shifting) {
+          const float in_front = first ? before[s][j] : before[s][j] * inv_p * w[s][j];
+          r = y + (in_front - y) * mix[s][j];
+          kept_row.v[j] = lrow != nullptr ? final_row[s][j] * inv_l * w[s][j] : y;
+        }
+        result.v[j] = from_float<OUT>(r);
+      }
+      if (first) *reinterpret_cast<Quad4<float>*>(srow + i) = kept_row;
+      *reinterpret_cast<Quad4<OUT>*>(orow + i) = result;
+    }
+    return;
+  }
+  if (KEPT == 1) {
     float mine[SN_KEEP], before[SN_KEEP], final_row[SN_KEEP], w[SN_KEEP], mix[SN_KEEP];
 #pragma unroll
     for (int s = 0; s < SN_KEEP; ++s) {
@@ -130,11 +205,17 @@ template <typename IN, typename OUT, typename W>
 static cudaError_t launch_rms_norm_shift(void* out, const void* x, const void* w, const void* shift, float* state,
                                          const int* req_index, const int* query_start, const int* slots, int rows,
                                          int width, float eps, cudaStream_t stream) {
-  if (width <= SN_THREADS * SN_KEEP)
-    return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, true>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
+  auto on4 = [](const void* p, size_t size) { return (reinterpret_cast<uintptr_t>(p) % (4 * size)) == 0; };
+  if (width <= SN_THREADS * SN_KEEP && width % 4 == 0 && on4(out, sizeof(OUT)) && on4(x, sizeof(IN)) &&
+      on4(w, sizeof(W)) && (shift == nullptr || (on4(shift, sizeof(W)) && aligned16(state))))
+    return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, 2>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
                       (OUT*)out, (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots,
                       width, eps);
-  return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, false>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
+  if (width <= SN_THREADS * SN_KEEP)
+    return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, 1>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
+                      (OUT*)out, (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots,
+                      width, eps);
+  return kvb_launch((rms_norm_shift_kernel<IN, OUT, W, 0>), dim3(rows), dim3(SN_THREADS), 0, stream, true,
                     (OUT*)out, (const IN*)x, (const W*)w, (const W*)shift, state, req_index, query_start, slots,
                     width, eps);
 }
@@ -169,10 +250,6 @@ extern "C" int kvb_rms_norm_shift(void* out, const void* x, const void* weight, 
   KVB_CHECK_LAUNCH();
   return 0;
 }
-
-// Four neighbouring entries, loaded and stored as one access.
-template <typename T>
-struct __align__(4 * sizeof(T)) Quad4 { T v[4]; };
 
 // KEPT: 0 rows of any width, read twice; 1 rows up to SN_THREADS * SN_KEEP entries kept in registers; 2 the same
 // with four neighbouring entries a thread and access (widths that are multiples of 4, rows on 16-byte boundaries).

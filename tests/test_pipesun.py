@@ -216,6 +216,70 @@ def test_long_portions_on_carried_up_keys(case, minimum, tmp_path, monkeypatch):
         compare(rc.collect(steps, out, cfg["vocab"]), case["reference"], "bfloat16")
 
 
+def random_config(rng):
+    """A configuration drawn at random: order and kinds of layers, head counts, sizes (also ones no vector fits),
+    borrowed caches, layers without feed-forward."""
+    layers, owners = [], []
+    for index in range(rng.randint(2, 7)):
+        ff = None if rng.random() < 0.15 else rng.choice([20, 48, 64])
+        if rng.random() < 0.5:
+            if owners and rng.random() < 0.35:
+                source = rng.choice(owners)
+                m = layers[source]["mixer"]
+                layers.append(D(heads=m["kv_heads"] * rng.choice([1, 2, 3, 4]), kv_heads=m["kv_heads"], dim=m["dim"],
+                                vdim=m["vdim"], diff=rng.choice([0.1, 0.5, 0.8]), kv_from=source, ff=ff))
+            else:
+                kv_heads = rng.choice([1, 2, 4])
+                layers.append(D(heads=kv_heads * rng.choice([1, 2, 3, 4, 8]), kv_heads=kv_heads,
+                                dim=rng.choice([16, 20, 32, 48, 64, 80, 128]), vdim=rng.choice([8, 12, 16, 24, 48, 64, 160, 256]),
+                                diff=rng.choice([0.1, 0.5, 0.8]), ff=ff))
+                owners.append(index)
+        else:
+            rot = rng.choice([0, 4, 8, 16, 32, 64])
+            layers.append(L(heads=rng.choice([1, 2, 3, 4, 8, 16, 24]), dim=rng.choice([8, 16, 32, 64, 128]), rot_dim=rot,
+                            rot_dims=rot if rng.random() < 0.7 else rng.choice(range(0, rot + 1, 2)),
+                            vdim=rng.choice([8, 16, 32, 72, 128]), kv_rank=rng.choice([8, 24, 32, 64, 128, 256, 512]),
+                            base=rng.choice([50.0, 10000.0]), ff=ff))
+    return P.model_config(layers, vocab=rng.randint(50, 300), width=rng.choice([32, 40, 48, 64, 96, 128]),
+                          eps=rng.choice([1e-5, 1e-6]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", [3, 11, 20, 37])
+def test_configurations_drawn_at_random(seed, tmp_path, monkeypatch):
+    """32-bit: the mixed cutting against the plain statement.  bfloat16: what a random model loses depends on the
+    model, so the yardstick is the same model on the general kernels alone (they round where the fast ones do,
+    but for the probabilities): the tensor-core kernels and the carried-up reading may not lose noticeably more."""
+    import random
+
+    import kvcore_b200.kernels.api as api
+    from kvcore_b200.parts.attention_maps import LatentAttention
+
+    rng = random.Random(seed)
+    cfg = random_config(rng)
+    weights = write_folder(tmp_path / "m", cfg, seed)
+    requests = {f"q{i}": rc.random_tokens(cfg["vocab"], rng.choice([1, 2, 17, 60, 140, 200]), 10 * seed + i) for i in range(5)}
+    reference = {rid: P.forward(cfg, weights, toks).numpy() for rid, toks in requests.items()}
+    steps = rc.trace_mixed(requests, max_live=4, seed=seed)
+
+    def worst_and_median(name, dtype):
+        out = tmp_path / name
+        rc.run_inprocess(tmp_path / "m", dtype, steps, out, rc.peak_tokens(steps), device="cuda:0",
+                         fill_freed_pages="poison")
+        rows = rc.collect(steps, out, cfg["vocab"])
+        assert all(np.isfinite(row).all() for row in rows.values())
+        rms = [np.sqrt(np.mean((row - reference[rid][pos]) ** 2)) / reference[rid].std() for (rid, pos), row in rows.items()]
+        return max(rms), float(np.median(rms))
+
+    assert worst_and_median("exact", "float32")[0] <= 5e-5
+    monkeypatch.setattr(LatentAttention, "expand_min_tokens", rng.choice([16, 128]))
+    fast = worst_and_median("fast", "bfloat16")
+    monkeypatch.setattr(api, "flash_dims_supported", lambda *args, **kwargs: False)
+    monkeypatch.setattr(LatentAttention, "expand_min_tokens", 1 << 30)
+    general = worst_and_median("general", "bfloat16")
+    assert fast[0] <= 1.5 * general[0] + 1e-2 and fast[1] <= 1.5 * general[1] + 5e-3, (fast, general)
+
+
 def test_residual_stream_after_every_layer(case, device):
     """Layer by layer: the 32-bit stream that each block hands on against the plain statement's."""
     from kvcore_b200.engine.step import StepEntry
